@@ -1,0 +1,329 @@
+#!/usr/bin/env python
+"""Benchmark of the HTR-W1 packed-linear decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Metric: packed-weight GB/s of the batch-1 packed GEMV (bytes = m*n*K/8 + 2m + n/8 + m/8 per linear,
+docs/METHODOLOGY.md:89 of the reference).  Workload "mlp_bitrate_sweep_batch1": the MLP-shaped linears
+12288x4096 and 4096x12288 at K2, K3, K4 and K5, batch 1, bf16 activations ~N(0,1), synthetic packed weights
+(uniform random words are valid streams; throughput is data-independent).  Each (shape, K) exists in COPIES
+distinct copies so that every K-group alone is larger than the 126 MB L2: one step is one pass over all of
+them, so no launch finds its weights in cache.
+
+One JSON line is printed by rank 0:
+  value     device-resident throughput of the whole pass, CUDA-event timed, max over ranks
+  e2e       the same pass through the public operator (htr_b200.ops.linear) with the activations in pinned
+            host memory and the outputs copied back to pinned host memory inside the timed region
+  roofline  of the GEMV kernel: achieved = algorithmic packed bytes per launch / average launch duration,
+            peak = measured HBM copy bandwidth (MEASURED_PEAKS.json, else the fallback 6650 GB/s)
+  cpu_baseline  the CPU restatement of the reference's decode + matmul path (oracle/, OpenMP) on a bounded
+            sample of the same linears, timed on the host cores of this box
+With N > 1 every rank holds its own row shard of N-times taller linears (weak scaling); the bf16 outputs are
+all-gathered over NCCL.  `--impl reference` times only the CPU path (rank 0).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = ((12288, 4096), (4096, 12288))      # (m out, n in): up/gate-like and down-like MLP linears
+WIDTHS = (2, 3, 4, 5)
+COPIES = 8
+FALLBACK_HBM_GBS = 6650.0
+
+
+def payload_bytes(m, n, K):
+    return m * n * K // 8 + 2 * m + n // 8 + m // 8
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle sampling during the timed region (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                c = [t.strip() for t in line.split(",")]
+                if len(c) < 9:
+                    continue
+                try:
+                    sm.append(float(c[1]))
+                    mx.append(float(c[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_sample(threads=None, repeats=1):
+    """Decode + matmul of one linear per (shape, K) on the host cores with the CPU oracle (the port of the
+    reference's wire.dequant + matmul).  Returns (GB/s, seconds, threads, description)."""
+    import numpy as np
+    from oracle import oracle as O
+
+    O.build()
+    c = O.COracle()
+    threads = threads or os.cpu_count()
+    rng = np.random.default_rng(0)
+    cases = []
+    for (m, n) in SHAPES:
+        for K in WIDTHS:
+            qw = rng.integers(-2 ** 31, 2 ** 31, size=(m // 16, n // 16, 8 * K), dtype=np.int64).astype(np.int32)
+            sc = (np.abs(rng.standard_normal(m)) * 0.01 + 0.01).astype(np.float16)
+            su = rng.integers(0, 256, n // 8).astype(np.uint8)
+            sv = rng.integers(0, 256, m // 8).astype(np.uint8)
+            x = rng.standard_normal((1, n)).astype(np.float32)
+            cases.append((x, qw, sc, su, sv, payload_bytes(m, n, K)))
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(repeats):
+        for x, qw, sc, su, sv, b in cases:
+            c.linear(x, qw, sc, su, sv, threads=threads)
+            nbytes += b
+    dt = time.perf_counter() - t0
+    return nbytes / dt / 1e9, dt, threads, f"{repeats} pass(es) over one linear per (shape,K): {len(cases)} linears, {nbytes / 1e6:.1f} MB packed"
+
+
+def base_line(args, impl=None):
+    d = {"metric": "packed_gemv_weight_GBps_batch1", "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+         "config": {"workload": "mlp_bitrate_sweep_batch1", "shapes_m_x_n": [list(s) for s in SHAPES], "K": list(WIDTHS), "batch": 1,
+                    "copies_per_shape_and_K": COPIES, "activations": "bf16 N(0,1)",
+                    "l2_policy": "inputs larger than L2: every K-group of a pass holds >= 201 MB of distinct packed weights",
+                    "sharding": "rows" if args.gpus > 1 else "none"}}
+    if impl:
+        d["impl"] = impl
+    return d
+
+
+def run_reference(args):
+    """CPU arm: every step is one bounded sample (one linear per shape and K) on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(min(args.warmup, 1)):          # the CPU path has nothing to warm beyond a first pass
+        cpu_sample()
+    vals, secs = [], []
+    for _ in range(args.steps):
+        gbs, dt, threads, sample = cpu_sample()
+        vals.append(gbs)
+        secs.append(dt)
+    v = sum(1.0 for _ in vals) / sum(1.0 / g for g in vals)       # bytes per step are equal: harmonic mean = total bytes / total time
+    line = base_line(args, "reference")
+    line.update(value=v, ms_per_step=1e3 * statistics.mean(secs), gpu_launches=0,
+                cpu_baseline={"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample + " per step"},
+                e2e={"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from htr_b200 import ops, wire
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- synthetic packed linears, resident in HBM (each rank: its own row shard of an N-times taller linear)
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    groups = []          # per K: list of (x, qw, sc, su, sv, y_gathered or None)
+    total_bytes, launches = 0, 0
+    for K in WIDTHS:
+        items = []
+        for c in range(COPIES):
+            for (m, n) in SHAPES:
+                qw = torch.randint(-2 ** 31, 2 ** 31, (m // 16, n // 16, 8 * K), dtype=torch.int32, device=dev, generator=g)
+                sc = (torch.randn(m, device=dev, generator=g).abs() * 0.01 + 0.01).half()
+                su = torch.randint(0, 256, (n // 8,), dtype=torch.uint8, device=dev, generator=g)
+                sv = torch.randint(0, 256, (m // 8,), dtype=torch.uint8, device=dev, generator=g)
+                x = torch.randn(1, n, device=dev, generator=g).bfloat16()
+                gathered = torch.empty(world, m, dtype=torch.bfloat16, device=dev) if world > 1 else None
+                items.append((x, qw, sc, su, sv, gathered))
+                total_bytes += payload_bytes(m, n, K)
+                launches += 1
+        groups.append(items)
+
+    def run_group(items):
+        for x, qw, sc, su, sv, gathered in items:
+            y = ops.linear(x, qw, sc, su, sv)
+            if gathered is not None:
+                dist.all_gather_into_tensor(gathered, y)
+
+    # warm every kernel and the workspace, then capture one CUDA graph per K-group
+    for items in groups:
+        run_group(items)
+    torch.cuda.synchronize()
+    graphs = []
+    use_graphs = world == 1 and not args.no_graphs
+    if use_graphs:
+        for items in groups:
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                run_group(items)
+            graphs.append(gr)
+
+    def one_pass(marks=None):
+        for i, items in enumerate(groups):
+            if marks is not None:
+                marks[i][0].record()
+            if use_graphs:
+                graphs[i].replay()
+            else:
+                run_group(items)
+            if marks is not None:
+                marks[i][1].record()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(3, args.warmup)):
+        one_pass()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    marks = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in groups] for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for s in range(args.steps):
+        one_pass(marks[s])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    per_k_ms = [sum(marks[s][i][0].elapsed_time(marks[s][i][1]) for s in range(args.steps)) / args.steps for i in range(len(groups))]
+
+    # ---- end to end through the public operator: activations from pinned host memory, outputs back to the host
+    host_x = [[it[0].cpu().pin_memory() for it in items] for items in groups]
+    host_y = [[torch.empty(1, it[1].shape[0] * 16, dtype=torch.bfloat16).pin_memory() for it in items] for items in groups]
+    h2d = sum(t.numel() * 2 for row in host_x for t in row)
+    d2h = sum(t.numel() * 2 for row in host_y for t in row)
+
+    def e2e_pass():
+        for gi, items in enumerate(groups):
+            for li, (x, qw, sc, su, sv, gathered) in enumerate(items):
+                xd = host_x[gi][li].to(dev, non_blocking=True)
+                y = ops.linear(xd, qw, sc, su, sv)
+                if gathered is not None:
+                    dist.all_gather_into_tensor(gathered, y)
+                host_y[gi][li].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        e2e_pass()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(1, min(args.steps, 10))
+    f0.record()
+    for _ in range(e2e_steps):
+        e2e_pass()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms] + per_k_ms, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms, per_k_ms = float(t[0]), float(t[1]), [float(v) for v in t[2:]]
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        job_bytes = total_bytes * world
+        value = job_bytes * args.steps / (ms * 1e-3) / 1e9
+        e2e_value = job_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+        per_k = {}
+        for i, K in enumerate(WIDTHS):
+            kb = sum(payload_bytes(m, n, K) for (m, n) in SHAPES) * COPIES
+            gbs = kb / (per_k_ms[i] * 1e-3) / 1e9
+            per_k[f"K{K}"] = {"GBps_per_gpu": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                              "us_per_launch": round(1e3 * per_k_ms[i] / (len(SHAPES) * COPIES), 3)}
+        achieved = total_bytes * args.steps / (ms * 1e-3) / 1e9     # per GPU: one kernel family, launches back to back
+        line = base_line(args)
+        line.update(value=value, ms_per_step=ms / args.steps, gpu_launches=launches * args.steps, clocks=clocks,
+                    e2e={"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+                    roofline={"bound": "hbm", "kernel": "packed_gemv_kernel<K,1>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                              "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                              "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / launches,
+                              "per_K": per_k},
+                    timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs else "eager launches"))
+        if world == 1 and not args.no_cpu:
+            gbs, dt, threads, sample = cpu_sample()
+            line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,56 @@
+"""ctypes binding of libhtr_b200.so (the C interface declared in include/htr_b200.h).
+
+There is no fallback: if the shared library has not been built (`python -m htr_b200.build`) importing
+this module raises, and every operator of the package fails with it.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhtr_b200.so")
+
+BF16, F16, F32 = 0, 1, 2
+GEMV_MAX_ROWS = 8
+
+EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
+           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_dequant_w",
+           "htr_set_gemv_ctas_per_sm", "htr_linear_plan")
+
+
+class HTRError(RuntimeError):
+    """A C entry point returned a negative status (the reference raises RuntimeError from TORCH_CHECK)."""
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m htr_b200.build` (nvcc, sm_100a). "
+                          "htr_b200 has no CPU or eager fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_size_t
+    lib.htr_status_string.restype = ctypes.c_char_p
+    lib.htr_status_string.argtypes = [i32]
+    lib.htr_last_cuda_error.restype = i32
+    lib.htr_version.restype = i32
+    lib.htr_decode_raw.argtypes = [vp, i64, i32, vp, vp]
+    lib.htr_rht.argtypes = [vp, i32, i32, i32, vp, vp, vp]
+    lib.htr_linear_workspace_bytes.restype = sz
+    lib.htr_linear_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.htr_linear_counter_bytes.restype = sz
+    lib.htr_linear_counter_bytes.argtypes = [i32]
+    lib.htr_linear.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.htr_dequant_w.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, i32, vp]
+    lib.htr_set_gemv_ctas_per_sm.restype = None
+    lib.htr_set_gemv_ctas_per_sm.argtypes = [i32]
+    lib.htr_linear_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
+    return lib
+
+
+lib = _load()
+
+
+def check(status, what):
+    if status != 0:
+        msg = lib.htr_status_string(status).decode()
+        if status == -7:
+            msg += f" (cudaError {lib.htr_last_cuda_error()})"
+        raise HTRError(f"{what}: {msg}")

@@ -1,0 +1,228 @@
+// C interface of the library: argument checks, launch planning and dispatch to the kernels.
+#include <cmath>
+#include <cstdlib>
+#include <mutex>
+
+#include "packed_gemv.cuh"
+
+namespace htr {
+int run_decode_raw(int K, const uint32_t* qw, int16_t* out, long long ntiles, cudaStream_t st);
+int run_rht(const void* x, int dtype, int M, int n, const uint8_t* su, float* xt, cudaStream_t st);
+int run_dequant_w(int K, const uint32_t* qw, const __half* scales, const uint8_t* su, const uint8_t* sv, float cb, void* W,
+                  int out_dtype, int mt, int nt, cudaStream_t st);
+
+static thread_local int t_last_cuda = 0;
+static int g_ctas_override = 0;
+
+static int cuda_fail(int e) {
+  t_last_cuda = e;
+  return HTR_ERR_CUDA;
+}
+
+static bool width_ok(int K) { return K == 2 || K == 3 || K == 4 || K == 5 || K == 6 || K == 8; }
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// 1/sqrt(mean v(s)^2) over all 65536 states in double (htr/wire.py:27-30), evaluated once
+static double codebook_scale() {
+  static const double value = [] {
+    double acc = 0.0;
+    for (uint32_t s = 0; s < 65536u; ++s) {
+      const double v = (double)code_value(s);
+      acc += v * v;
+    }
+    return 1.0 / std::sqrt(acc / 65536.0);
+  }();
+  return value;
+}
+
+static int template_rows(int M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8; }
+
+static int gemv_ctas_per_sm(int K, int mt_rows) {
+  switch (K) {
+    case 2: return packed_gemv_ctas_per_sm<2>(mt_rows);
+    case 3: return packed_gemv_ctas_per_sm<3>(mt_rows);
+    case 4: return packed_gemv_ctas_per_sm<4>(mt_rows);
+    case 5: return packed_gemv_ctas_per_sm<5>(mt_rows);
+    case 6: return packed_gemv_ctas_per_sm<6>(mt_rows);
+    case 8: return packed_gemv_ctas_per_sm<8>(mt_rows);
+  }
+  return -1;
+}
+
+struct Plan {
+  int grid, slots, rows_t;
+  long long units;
+  int cg, rbs;
+};
+
+// device facts are cached per device; the occupancy of each instantiation is cached per (device, K, rows)
+static int device_sms(int dev) {
+  static int cache[64] = {0};
+  if (dev >= 0 && dev < 64 && cache[dev]) return cache[dev];
+  int v = 0;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+  if (dev >= 0 && dev < 64) cache[dev] = v;
+  return v;
+}
+
+static int cached_occupancy(int dev, int K, int rows_t) {
+  static int cache[64][9][9] = {{{0}}};
+  static std::mutex mu;
+  if (dev < 0 || dev >= 64) return gemv_ctas_per_sm(K, rows_t);
+  std::lock_guard<std::mutex> lock(mu);
+  int& slot = cache[dev][K][rows_t];
+  if (slot == 0) slot = gemv_ctas_per_sm(K, rows_t);
+  return slot;
+}
+
+static int make_plan(int M, int m, int n, int K, Plan* out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail((int)e);
+  const int sms = device_sms(dev);
+  if (sms <= 0) return cuda_fail((int)cudaErrorInvalidDevice);
+  Plan pl;
+  pl.rows_t = template_rows(M);
+  int per_sm = g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
+  if (per_sm <= 0) return cuda_fail((int)cudaErrorLaunchOutOfResources);
+  pl.rbs = m / 128;
+  pl.cg = n / 64;
+  pl.units = (long long)pl.rbs * pl.cg;
+  long long grid = (long long)sms * per_sm;
+  if (grid > pl.units) grid = pl.units;
+  pl.grid = (int)grid;
+  // a row block holds cg units and a CTA at least floor(U/G) of them
+  const long long per_cta = pl.units / pl.grid;
+  pl.slots = (int)((pl.cg + per_cta - 1) / per_cta) + 1;
+  *out = pl;
+  return HTR_OK;
+}
+
+static size_t counter_bytes(int m) { return (((size_t)(m / 128) * sizeof(int)) + 255) / 256 * 256; }
+
+}  // namespace htr
+
+using namespace htr;
+
+extern "C" {
+
+const char* htr_status_string(int status) {
+  switch (status) {
+    case HTR_OK: return "ok";
+    case HTR_ERR_BAD_K: return "unsupported bits per weight (K must be 2, 3, 4, 5, 6 or 8)";
+    case HTR_ERR_BAD_SHAPE: return "bad shape (m and n must be positive multiples of 128; row count out of range)";
+    case HTR_ERR_BAD_DTYPE: return "unsupported element type";
+    case HTR_ERR_WORKSPACE: return "workspace missing or too small";
+    case HTR_ERR_NULL: return "required pointer is NULL";
+    case HTR_ERR_ALIGNMENT: return "pointer is not 16-byte aligned";
+    case HTR_ERR_CUDA: return "CUDA runtime error";
+    case HTR_ERR_TOO_LARGE: return "size exceeds the limit of this entry point";
+  }
+  return "unknown status";
+}
+
+int htr_last_cuda_error(void) { return t_last_cuda; }
+int htr_version(void) { return 100; }
+
+void htr_set_gemv_ctas_per_sm(int ctas) { g_ctas_override = ctas > 0 ? ctas : 0; }
+
+int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream) {
+  if (!width_ok(K)) return HTR_ERR_BAD_K;
+  if (ntiles < 0 || ntiles > (1ll << 34)) return HTR_ERR_BAD_SHAPE;
+  if (ntiles == 0) return HTR_OK;
+  if (!qweight || !out) return HTR_ERR_NULL;
+  if (!aligned16(qweight) || !aligned16(out)) return HTR_ERR_ALIGNMENT;
+  const int e = run_decode_raw(K, static_cast<const uint32_t*>(qweight), out, ntiles, static_cast<cudaStream_t>(stream));
+  return e ? cuda_fail(e) : HTR_OK;
+}
+
+int htr_rht(const void* x, int dtype, int M, int n, const uint8_t* su, float* xt, htr_stream_t stream) {
+  if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
+  if (M < 0 || n <= 0 || n % 128) return HTR_ERR_BAD_SHAPE;
+  if (M == 0) return HTR_OK;
+  if (!x || !su || !xt) return HTR_ERR_NULL;
+  if (!aligned16(x) || !aligned16(xt)) return HTR_ERR_ALIGNMENT;
+  const int e = run_rht(x, dtype, M, n, su, xt, static_cast<cudaStream_t>(stream));
+  return e ? cuda_fail(e) : HTR_OK;
+}
+
+size_t htr_linear_counter_bytes(int m) { return m > 0 ? counter_bytes(m) : 0; }
+
+size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
+  if (!width_ok(K) || M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return 0;
+  Plan pl;
+  if (make_plan(M, m, n, K, &pl) != HTR_OK) return 0;
+  return counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
+}
+
+int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block) {
+  if (!width_ok(K)) return HTR_ERR_BAD_K;
+  if (M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return HTR_ERR_BAD_SHAPE;
+  Plan pl;
+  const int rc = make_plan(M, m, n, K, &pl);
+  if (rc != HTR_OK) return rc;
+  if (grid) *grid = pl.grid;
+  if (slots_per_block) *slots_per_block = pl.slots;
+  return HTR_OK;
+}
+
+int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+               const uint8_t* sv, const void* bias, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+  if (!width_ok(K)) return HTR_ERR_BAD_K;
+  if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
+  if (M < 0 || M > HTR_GEMV_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
+  if ((long long)mt * 16 > 0x7FFFFFFFll / 2 || (long long)nt * 16 > 0x7FFFFFFFll / 2) return HTR_ERR_TOO_LARGE;
+  if (M == 0) return HTR_OK;
+  if (!x || !qweight || !scales || !su || !sv || !y) return HTR_ERR_NULL;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(y) || (bias && !aligned16(bias)) || !aligned16(workspace)) return HTR_ERR_ALIGNMENT;
+  const int m = mt * 16, n = nt * 16;
+  Plan pl;
+  const int rc = make_plan(M, m, n, K, &pl);
+  if (rc != HTR_OK) return rc;
+  const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
+  if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
+
+  GemvParams p;
+  p.x = x;
+  p.qw = static_cast<const uint32_t*>(qweight);
+  p.scales = static_cast<const __half*>(scales);
+  p.su = su;
+  p.sv = sv;
+  p.bias = bias;
+  p.y = y;
+  p.counters = static_cast<int*>(workspace);
+  p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counter_bytes(m));
+  p.rows = M;
+  p.mt = mt;
+  p.nt = nt;
+  p.dtype = dtype;
+  p.cg = pl.cg;
+  p.units = pl.units;
+  p.slots = pl.slots;
+  p.cb = (float)codebook_scale();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int e = 0;
+  switch (K) {
+    case 2: e = launch_packed_gemv<2>(p, pl.rows_t, pl.grid, st); break;
+    case 3: e = launch_packed_gemv<3>(p, pl.rows_t, pl.grid, st); break;
+    case 4: e = launch_packed_gemv<4>(p, pl.rows_t, pl.grid, st); break;
+    case 5: e = launch_packed_gemv<5>(p, pl.rows_t, pl.grid, st); break;
+    case 6: e = launch_packed_gemv<6>(p, pl.rows_t, pl.grid, st); break;
+    case 8: e = launch_packed_gemv<8>(p, pl.rows_t, pl.grid, st); break;
+  }
+  return e ? cuda_fail(e) : HTR_OK;
+}
+
+int htr_dequant_w(const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su, const uint8_t* sv, void* W,
+                  int out_dtype, htr_stream_t stream) {
+  if (!width_ok(K)) return HTR_ERR_BAD_K;
+  if (out_dtype < HTR_DTYPE_BF16 || out_dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
+  if (mt <= 0 || nt <= 0 || mt % 8 || nt % 8 || mt / 8 > 65535) return HTR_ERR_BAD_SHAPE;
+  if (!qweight || !scales || !su || !sv || !W) return HTR_ERR_NULL;
+  if (!aligned16(qweight) || !aligned16(W)) return HTR_ERR_ALIGNMENT;
+  const int e = run_dequant_w(K, static_cast<const uint32_t*>(qweight), static_cast<const __half*>(scales), su, sv,
+                              (float)codebook_scale(), W, out_dtype, mt, nt, static_cast<cudaStream_t>(stream));
+  return e ? cuda_fail(e) : HTR_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+"""Operator boundary of the packed linear: `linear()` and the torch custom op `htr::linear`.
+
+Same signature and meaning as htr/ops.py:107-122 of the reference, so a caller (the vLLM quantization
+method, or any torch code) switches by importing this module instead.  The dispatch policy is re-derived
+for one B200 (148 SMs, HBM3e) rather than copied from the 40-CU part the reference was tuned on:
+
+  M == 0            empty result                                             (htr/ops.py:73-74)
+  1 <= M <= 8       one launch of the streaming GEMV (activation transform, decode + dot, split reduce,
+                    output transform fused)                                  (replaces htr/ops.py:75-76,95-101)
+  8 <  M <= LOOP    the same kernel over 8-row chunks                        (htr/ops.py:77-88)
+  M > LOOP          original-basis bf16 weight from the dequant kernel, then a library GEMM
+                                                                             (htr/ops.py:89-93)
+
+All work is enqueued on the current torch stream without a host synchronisation, so the op can be
+captured in a CUDA graph.  Nothing here runs on the CPU: without the CUDA library the import fails.
+"""
+import os
+
+import torch
+
+from . import _lib, wire
+
+CB = wire.cbscale()
+GEMV_MAX_M = _lib.GEMV_MAX_ROWS
+GEMV_LOOP_MAX = int(os.environ.get("HTR_GEMV_LOOP_MAX", "64"))
+
+_DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+_WORKSPACES = {}
+_MIN_WORKSPACE = 1 << 22
+
+
+def workspace(device, nbytes, stream=None):
+    """Scratch of the GEMV (split partial sums + arrival counters), one per (device, stream).
+
+    The counters at its start must be zero before first use and every launch leaves them zero, so the buffer
+    is zero-filled once and then reused (the reference keeps a per-device `counters` tensor the same way,
+    htr/ops.py:24-28).  Calls on different streams get different buffers."""
+    stream = torch.cuda.current_stream(device).cuda_stream if stream is None else stream
+    key = (device.index, stream)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        size = max(_MIN_WORKSPACE, 1 << (int(nbytes) - 1).bit_length())
+        buf = torch.zeros(size, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def _check(x2, qweight, scales, su, sv, bias):
+    if not x2.is_cuda:
+        raise _lib.HTRError("htr::linear has no CPU path: tensors must live on a CUDA device")
+    if x2.dtype not in _DTYPES:
+        raise _lib.HTRError(f"htr::linear: unsupported activation dtype {x2.dtype}")
+    if qweight.dtype != torch.int32 or qweight.dim() != 3 or qweight.shape[2] % 8:
+        raise _lib.HTRError("htr::linear: qweight must be int32 [m/16, n/16, 8K]")
+    mt, nt, W = qweight.shape
+    if x2.shape[1] != nt * 16:
+        raise _lib.HTRError(f"htr::linear: activations have {x2.shape[1]} columns, the weight expects {nt * 16}")
+    if scales.dtype != torch.float16 or scales.numel() != mt * 16:
+        raise _lib.HTRError("htr::linear: scales must be float16 [m]")
+    if su.dtype != torch.uint8 or su.numel() != nt * 2 or sv.dtype != torch.uint8 or sv.numel() != mt * 2:
+        raise _lib.HTRError("htr::linear: su / sv must be uint8 [n/8] / [m/8]")
+    if bias is not None and (bias.dtype != x2.dtype or bias.numel() != mt * 16):
+        raise _lib.HTRError("htr::linear: bias must have the activation dtype and m elements")
+
+
+def _gemv(x2, qweight, scales, su, sv, bias, out):
+    """One C call: rows of x2 (<= 8) against the packed weight, result written into `out`."""
+    M = x2.shape[0]
+    mt, nt, W = qweight.shape
+    K = W // 8
+    need = _lib.lib.htr_linear_workspace_bytes(M, mt * 16, nt * 16, K)
+    if need == 0:
+        _lib.check(_lib.lib.htr_linear_plan(M, mt * 16, nt * 16, K, None, None), "htr_linear")
+    ws = workspace(x2.device, need)
+    st = torch.cuda.current_stream(x2.device).cuda_stream
+    rc = _lib.lib.htr_linear(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
+                             sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st)
+    _lib.check(rc, "htr_linear")
+
+
+def _linear_impl(x2, qweight, scales, su, sv, bias):
+    _check(x2, qweight, scales, su, sv, bias)
+    M = x2.shape[0]
+    mt = qweight.shape[0]
+    if M == 0:
+        return x2.new_empty((0, mt * 16))
+    qweight, scales, su, sv = qweight.contiguous(), scales.contiguous(), su.contiguous(), sv.contiguous()
+    bias = None if bias is None else bias.contiguous()
+    with torch.cuda.device(x2.device):
+        if M <= GEMV_LOOP_MAX:
+            y = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
+            for r0 in range(0, M, GEMV_MAX_M):
+                r1 = min(M, r0 + GEMV_MAX_M)
+                _gemv(x2[r0:r1], qweight, scales, su, sv, bias, y[r0:r1])
+            return y
+        W = wire.dequant(qweight, scales, su, sv, dtype=torch.bfloat16 if x2.dtype == torch.float32 else x2.dtype)
+        return torch.nn.functional.linear(x2, W.to(x2.dtype), bias)
+
+
+@torch.library.custom_op("htr::linear", mutates_args=())
+def htr_linear_op(x2: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, su: torch.Tensor, sv: torch.Tensor,
+                  bias: torch.Tensor | None) -> torch.Tensor:
+    return _linear_impl(x2.contiguous(), qweight, scales, su, sv, bias)
+
+
+@htr_linear_op.register_fake
+def _(x2, qweight, scales, su, sv, bias):
+    return x2.new_empty((x2.shape[0], qweight.shape[0] * 16))
+
+
+def linear(x, qweight, scales, su, sv, bias=None):
+    """y = x @ W^T (+ bias) for an HTR-W1 weight; x [..., n] -> [..., m] in x.dtype (htr/ops.py:118-122)."""
+    lead = x.shape[:-1]
+    y = htr_linear_op(x.reshape(-1, x.shape[-1]), qweight, scales, su, sv, bias)
+    return y.reshape(*lead, qweight.shape[0] * 16)

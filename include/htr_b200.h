@@ -1,0 +1,89 @@
+/*
+ * htr_b200 -- C interface of the B200 (sm_100a) packed-linear library for HTR-W1 weights.
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA stream
+ * without synchronising the host, and returns HTR_OK or a negative status; nothing aborts.
+ * Each declaration names the interface of the reference (HawgAuto/HTR) that it stands in for.
+ *
+ * Tensor contract (docs/FORMAT.md:25-32 of the reference):
+ *   qweight  int32/uint32 [m/16, n/16, 8*K] contiguous, 16-byte aligned; K in {2,3,4,5,6,8}
+ *   scales   float16 [m]            su  uint8 [n/8]           sv  uint8 [m/8]
+ *   m % 128 == 0 and n % 128 == 0.  Activations / outputs are row-major [M, n] / [M, m].
+ */
+#ifndef HTR_B200_H_
+#define HTR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes (0 = success; the reference raises RuntimeError from TORCH_CHECK, htr_kernels.cu:910-915) */
+enum {
+  HTR_OK = 0,
+  HTR_ERR_BAD_K = -1,        /* K outside {2,3,4,5,6,8} */
+  HTR_ERR_BAD_SHAPE = -2,    /* m or n not a multiple of 128, negative sizes, M out of range */
+  HTR_ERR_BAD_DTYPE = -3,    /* dtype not one of HTR_DTYPE_* */
+  HTR_ERR_WORKSPACE = -4,    /* workspace missing or smaller than htr_linear_workspace_bytes() */
+  HTR_ERR_NULL = -5,         /* a required pointer is NULL */
+  HTR_ERR_ALIGNMENT = -6,    /* a pointer is not 16-byte aligned */
+  HTR_ERR_CUDA = -7,         /* a CUDA runtime call failed; see htr_last_cuda_error() */
+  HTR_ERR_TOO_LARGE = -8     /* size beyond what the entry point supports */
+};
+
+/* activation / output element types; numbering follows the reference's out_dtype (htr/ops.py:79) */
+enum { HTR_DTYPE_BF16 = 0, HTR_DTYPE_F16 = 1, HTR_DTYPE_F32 = 2 };
+
+/* largest activation row count a single htr_linear call accepts through the streaming GEMV kernel */
+#define HTR_GEMV_MAX_ROWS 8
+
+typedef void* htr_stream_t; /* a cudaStream_t (NULL = the legacy default stream) */
+
+const char* htr_status_string(int status);
+int htr_last_cuda_error(void);  /* cudaError_t of the most recent HTR_ERR_CUDA on the calling thread */
+int htr_version(void);
+
+/* Integer codebook values of every tile, int16 [ntiles, 256] in stream order.
+ * Stands in for decode_raw (htr/csrc/htr_kernels.cpp:4, kernel k_decode_raw htr_kernels.cu:153-172);
+ * must equal wire.gen_values(wire.unpack_states(words, K)) bit for bit (htr/wire.py:10-13,54-63). */
+int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream);
+
+/* Activation transform xt = blockdiag(H128/sqrt(128)) (su * x), float32 [M, n].
+ * Stands in for prologue (htr_kernels.cpp:5, k_prologue htr_kernels.cu:189-234); unlike the reference it
+ * keeps float32 and needs no per-token range scale.  Reference math: docs/FORMAT.md:8. */
+int htr_rht(const void* x, int dtype, int M, int n, const uint8_t* su, float* xt, htr_stream_t stream);
+
+/* Bytes of scratch one htr_linear call with these sizes may touch (partial sums of the column splits and
+ * one arrival counter per 128-row block).  The first htr_linear_counter_bytes(m) bytes hold the counters:
+ * they must be zero before the first call and every call leaves them zero again.  One workspace may be
+ * shared by calls that are ordered on one stream; concurrent streams need one each.
+ * Stands in for the per-call `part` allocation and the persistent `counters` tensor (htr/ops.py:24-28). */
+size_t htr_linear_workspace_bytes(int M, int m, int n, int K);
+size_t htr_linear_counter_bytes(int m);
+
+/* y[M, m] = x[M, n] @ W^T (+ bias) for one HTR-W1 weight, y/bias in the dtype of x.  One launch: input
+ * sign flip + Hadamard, streaming decode of the trellis words with the dot products, split reduction,
+ * row scales, output Hadamard, output signs, bias, cast.  1 <= M <= HTR_GEMV_MAX_ROWS (M == 0 returns at once).
+ * Stands in for the decode branch of _linear_impl (htr/ops.py:69-101): prologue + gemv_epi / gemv_fused
+ * (htr_kernels.cu:337-652).  Must match x.float() @ wire.dequant(...).T (htr/wire.py:105-113). */
+int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+               const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
+               size_t workspace_bytes, htr_stream_t stream);
+
+/* Original-basis weight W = Sv Ho Q Hi Su as bf16 / f16 / f32 [m, n] (debug and prefill hook).
+ * Stands in for dequant_w (htr_kernels.cpp:13, k_dequant_w* htr_kernels.cu:658-903); compared with
+ * wire.dequant (htr/wire.py:105-113). */
+int htr_dequant_w(const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su, const uint8_t* sv,
+                  void* W, int out_dtype, htr_stream_t stream);
+
+/* Launch-shape knobs of htr_linear for measurements (0 = library default): CTAs per SM of the GEMV grid. */
+void htr_set_gemv_ctas_per_sm(int ctas);
+/* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */
+int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HTR_B200_H_ */
