@@ -49,9 +49,17 @@ static int gemv_ctas_per_sm(int K, int mt_rows) {
   return -1;
 }
 
+bool gemv_overlap_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("HTR_GEMV_OVERLAP");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
 struct Plan {
-  int grid, slots, rows_t;
-  long long units;
+  int grid, slots, rows_t, split;
+  int units;
   int cg, rbs;
 };
 
@@ -87,18 +95,30 @@ static int make_plan(int M, int m, int n, int K, Plan* out) {
   if (per_sm <= 0) return cuda_fail((int)cudaErrorLaunchOutOfResources);
   pl.rbs = m / 128;
   pl.cg = n / 64;
-  pl.units = (long long)pl.rbs * pl.cg;
-  long long grid = (long long)sms * per_sm;
-  if (grid > pl.units) grid = pl.units;
-  pl.grid = (int)grid;
-  // a row block holds cg units and a CTA at least floor(U/G) of them
-  const long long per_cta = pl.units / pl.grid;
-  pl.slots = (int)((pl.cg + per_cta - 1) / per_cta) + 1;
+  pl.units = pl.rbs * pl.cg;
+  const long long cap = (long long)sms * per_sm;          // CTAs that are resident together
+  // Short ranges: give every row block the same number of CTAs so that none crosses a row block (a crossing costs
+  // one extra publish + restage, which is only cheap when a CTA owns many units).  Otherwise: flat even ranges.
+  const long long flat_grid = cap < pl.units ? cap : pl.units;
+  if (pl.rbs <= cap && pl.units / flat_grid < 24) {
+    long long s = cap / pl.rbs;
+    if (s > pl.cg) s = pl.cg;
+    pl.split = (int)s;
+    pl.grid = pl.rbs * pl.split;
+    pl.slots = pl.split;
+  } else {
+    pl.split = 0;
+    pl.grid = (int)flat_grid;
+    // a row block holds cg units and a CTA at least floor(U/G) of them
+    const int per_cta = pl.units / pl.grid;
+    pl.slots = (pl.cg + per_cta - 1) / per_cta + 1;
+  }
   *out = pl;
   return HTR_OK;
 }
 
-static size_t counter_bytes(int m) { return (((size_t)(m / 128) * sizeof(int)) + 255) / 256 * 256; }
+// the counter region has one fixed size, so that calls of any shape share a workspace without moving it
+static size_t counter_bytes(int) { return (size_t)kCounterBytes; }
 
 }  // namespace htr
 
@@ -146,7 +166,7 @@ int htr_rht(const void* x, int dtype, int M, int n, const uint8_t* su, float* xt
   return e ? cuda_fail(e) : HTR_OK;
 }
 
-size_t htr_linear_counter_bytes(int m) { return m > 0 ? counter_bytes(m) : 0; }
+size_t htr_linear_counter_bytes(int m) { return counter_bytes(m); }
 
 size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
   if (!width_ok(K) || M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return 0;
@@ -168,13 +188,21 @@ int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block)
 
 int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
                const uint8_t* sv, const void* bias, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+  return htr_linear_ex(x, dtype, M, qweight, mt, nt, K, scales, su, sv, bias, y, workspace, workspace_bytes, stream, 0u);
+}
+
+int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                  const uint8_t* sv, const void* bias, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream,
+                  unsigned flags) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (M < 0 || M > HTR_GEMV_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
-  if ((long long)mt * 16 > 0x7FFFFFFFll / 2 || (long long)nt * 16 > 0x7FFFFFFFll / 2) return HTR_ERR_TOO_LARGE;
+  if (mt / 8 > kCounterBytes / 4 || (long long)(mt / 8) * (nt / 4) > 0x3FFFFFFFll) return HTR_ERR_TOO_LARGE;
   if (M == 0) return HTR_OK;
   if (!x || !qweight || !scales || !su || !sv || !y) return HTR_ERR_NULL;
-  if (!aligned16(x) || !aligned16(qweight) || !aligned16(y) || (bias && !aligned16(bias)) || !aligned16(workspace)) return HTR_ERR_ALIGNMENT;
+  if (!aligned16(x) || !aligned16(qweight) || !aligned16(y) || (bias && !aligned16(bias)) || !aligned16(workspace) ||
+      !aligned16(scales))
+    return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
   Plan pl;
   const int rc = make_plan(M, m, n, K, &pl);
@@ -198,6 +226,8 @@ int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int
   p.dtype = dtype;
   p.cg = pl.cg;
   p.units = pl.units;
+  p.split = pl.split;
+  p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
   p.slots = pl.slots;
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);

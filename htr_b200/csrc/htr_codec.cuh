@@ -55,10 +55,21 @@ HTR_HD uint32_t middle_bytes(uint32_t x) {  // bits 8..23 of x, zero-extended
 #endif
 }
 
+HTR_HD uint32_t bytesum_add_alu(uint32_t x, uint32_t acc) {  // same value through the byte-wise |a-b| sum (a different pipe)
+#if defined(__CUDA_ARCH__)
+  uint32_t d;
+  asm("vabsdiff4.u32.u32.u32.add %0, %1, %2, %3;" : "=r"(d) : "r"(x), "r"(0u), "r"(acc));
+  return d;
+#else
+  return acc + (x & 255u) + ((x >> 8) & 255u) + ((x >> 16) & 255u) + (x >> 24);
+#endif
+}
+
 // codebook integer of a 16-bit state
 HTR_HD int code_value(uint32_t s) { return (int)bytesum_add(s * kGenMul + kGenAdd, 0u) - 510; }
 // float32 bits of 12582912 + v(s): one multiply-add and one byte dot product, no conversion instruction
 HTR_HD uint32_t code_magic_bits(uint32_t s) { return bytesum_add(s * kGenMul + kGenAdd, kMagicBits - 510u); }
+HTR_HD uint32_t code_magic_bits_alu(uint32_t s) { return bytesum_add_alu(s * kGenMul + kGenAdd, kMagicBits - 510u); }
 
 // step distance of two states that sit side by side in one 32-bit window of the stream (K | 16), else 1
 template <int K>

@@ -5,19 +5,30 @@
 // (docs/FORMAT.md:7-13 of the reference; replaces its prologue + gemv_epi pair, htr/ops.py:95-98.)
 //
 // Decomposition.  The weight is cut into units of (128-row block) x (4 tile columns = 64 input columns);
-// unit u = rb * CG + cg.  The grid has G persistent CTAs and CTA b owns the contiguous unit range
-// [b*U/G, (b+1)*U/G), so every CTA streams the same number of packed bytes (+-1 unit) whatever the
-// shape.  A range may end inside a row block and continue in the next one.  For every row block it
-// touches, a CTA publishes one partial result [M,128]; the CTA that arrives last at the block's counter
-// adds the partials in CTA order (deterministic), applies row scales, the output Hadamard, output signs
-// and bias, and resets the counter.  No CTA ever waits for another one.
+// unit u = rb * CG + cg.  All CTAs of the grid are resident at once and each owns a contiguous unit range.
+// Short matrices use the "split" form: every row block is shared by exactly S CTAs, so no CTA crosses a
+// row block.  Tall matrices (more row blocks than resident CTAs, or long ranges) use the "flat" form:
+// CTA b owns [b*U/G, (b+1)*U/G), which may end inside a row block and continue in the next one.  For every
+// row block it touches, a CTA publishes one partial result [M,128]; the CTA that arrives last at the
+// block's counter adds the partials in CTA order (deterministic), applies row scales, the output
+// Hadamard, output signs and bias, and resets the counter.  No CTA ever waits for another one.
+//
+// Launch overlap.  The kernel is launched with programmatic stream serialisation: it starts while its
+// predecessor in the stream drains, prefetches its first packed words (weights never depend on earlier
+// kernels), and only then waits for the predecessor (griddepcontrol.wait) before it reads activations or
+// touches the workspace or the output.
 //
 // Inside a CTA (256 threads): warp = (half h of the row block: strips 4h..4h+3) x (tile column c of the
-// unit); lane = (strip g, row pair q).  Per unit a lane loads its K words (+1 history word from the
-// neighbouring lane), rebuilds 32 codebook integers in registers and multiplies them with the transformed
-// activations, which all lanes of the warp read from shared memory at the same address (broadcast).
-// The integer->float step uses the 1.5*2^23 bit trick; products are accumulated in float32 with the
-// packed two-wide FMA of sm_100.
+// unit); lane = (strip g, row pair q).  The packed words travel global -> shared memory through a ring of
+// kRing asynchronous copy stages per warp (16-byte cp.async, several units in flight per warp, no
+// registers held while they fly); a lane then reads its K words and the history word, rebuilds 32
+// codebook integers in registers and multiplies them with the transformed activations, which all lanes of
+// the warp read from shared memory at the same address (broadcast).
+//
+// Instruction budget.  On sm_100 the multiply-add of the hash, the byte dot product and the packed
+// two-wide float ops all issue to the same half-rate pipe, which is what bounds this kernel; the integer
+// to float step uses the exact 1.5*2^23 bit trick with packed adds and FMAs (half the issue slots of
+// scalar ones), and part of the byte sums are moved to the shift/logic pipe (see unit_fma).
 #pragma once
 #include "htr_codec.cuh"
 #include "htr_common.cuh"
@@ -25,8 +36,11 @@
 namespace htr {
 
 constexpr int kGemvThreads = 256;
-constexpr int kStageBlocks = 8;                  // 128-column blocks staged in shared memory at a time
+constexpr int kGemvWarps = kGemvThreads / 32;
+constexpr int kStageBlocks = 8;                  // 128-column blocks of activations staged at a time
 constexpr int kStageCols = kStageBlocks * 128;   // 1024 activations per row
+constexpr int kRing = 4;                         // asynchronous copy stages per warp
+constexpr int kCounterBytes = 1 << 16;           // arrival counters at the start of the workspace (16384 row blocks)
 
 struct GemvParams {
   const void* x;
@@ -42,32 +56,48 @@ struct GemvParams {
   int mt, nt;       // tiles along m and n
   int dtype;        // element type of x, y, bias
   int cg;           // column groups per row block (nt / 4)
-  long long units;  // row blocks * cg
+  int units;        // row blocks * cg
+  int split;        // > 0: every row block is shared by exactly `split` CTAs (grid = row blocks * split); 0: flat unit ranges
   int slots;        // partial slots per row block
+  int independent;  // 1: x, bias and y are untouched by the preceding kernel of the stream (wait only before publishing)
   float cb;         // 1 / rms of the codebook integers
 };
 
 // owner CTA of unit x when CTA b starts at floor(b*U/G)
 __device__ __host__ inline int unit_owner(long long x, long long G, long long U) { return (int)(((x + 1) * G - 1) / U); }
 
+// dynamic shared memory of one CTA: staged activations (reused for the reductions) + the copy ring
+template <int K, int MT>
+constexpr int gemv_smem_bytes() { return MT * kStageCols * 4 + kRing * kGemvWarps * 4 * (32 * K); }
+
+__device__ __forceinline__ void async_copy16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+// the K own words of row pair q and the history word, from a tile that sits in shared memory
 template <int K>
-__device__ __forceinline__ void load_unit_words(const uint32_t* __restrict__ p, uint32_t (&w)[K]) {
+__device__ __forceinline__ void read_unit_words(const uint32_t* __restrict__ tile, int q, uint32_t (&V)[K + 1]) {
+  const uint32_t* own = tile + q * K;
   if constexpr (K % 4 == 0) {
 #pragma unroll
     for (int i = 0; i < K / 4; ++i) {
-      const uint4 t = __ldg(reinterpret_cast<const uint4*>(p) + i);
-      w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
+      const uint4 t = *reinterpret_cast<const uint4*>(own + 4 * i);
+      V[4 * i + 1] = t.x; V[4 * i + 2] = t.y; V[4 * i + 3] = t.z; V[4 * i + 4] = t.w;
     }
   } else if constexpr (K % 2 == 0) {
 #pragma unroll
     for (int i = 0; i < K / 2; ++i) {
-      const uint2 t = __ldg(reinterpret_cast<const uint2*>(p) + i);
-      w[2 * i] = t.x; w[2 * i + 1] = t.y;
+      const uint2 t = *reinterpret_cast<const uint2*>(own + 2 * i);
+      V[2 * i + 1] = t.x; V[2 * i + 2] = t.y;
     }
   } else {
 #pragma unroll
-    for (int i = 0; i < K; ++i) w[i] = __ldg(p + i);
+    for (int i = 0; i < K; ++i) V[i + 1] = own[i];
   }
+  V[0] = tile[history_word<K>(q)];
 }
 
 // column of the tile stored at staged position pos (inverse of staged_col)
@@ -81,7 +111,11 @@ __device__ __forceinline__ constexpr int staged_col_inv(int pos) {
 
 // 32 weights x MT activation rows of one lane unit.  xs points at the 16 staged activations of this tile
 // for row 0; consecutive activation rows are kStageCols floats apart.
-template <int K, int MT>
+//
+// Pipe balance (measured on B200 with issue-rate probes): the hash multiply-add, the byte dot product and
+// the packed float ops share one half-rate pipe, the shifts/masks and the byte-wise |a-b| sum share another.
+// ALU4 of every 4 byte sums therefore go through the |a-b| form so that both pipes fill up together.
+template <int K, int MT, int ALU4 = 3>
 __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float* __restrict__ xs, float2 (&acc)[MT][2]) {
   uint32_t s[32];
   unit_states<K>(V, s);
@@ -96,8 +130,9 @@ __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float
       const int c0 = staged_col_inv<K>(quad * 4 + half * 2), c1 = staged_col_inv<K>(quad * 4 + half * 2 + 1);
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
-        const float2 w = __fadd2_rn(
-            make_float2(__uint_as_float(code_magic_bits(s[rr * 16 + c0])), __uint_as_float(code_magic_bits(s[rr * 16 + c1]))), unbias);
+        const uint32_t b0 = (2 * half + 2 * rr) % 4 < ALU4 ? code_magic_bits_alu(s[rr * 16 + c0]) : code_magic_bits(s[rr * 16 + c0]);
+        const uint32_t b1 = (2 * half + 2 * rr + 1) % 4 < ALU4 ? code_magic_bits_alu(s[rr * 16 + c1]) : code_magic_bits(s[rr * 16 + c1]);
+        const float2 w = __fadd2_rn(make_float2(__uint_as_float(b0), __uint_as_float(b1)), unbias);
 #pragma unroll
         for (int r = 0; r < MT; ++r) {
           const float2 xp = half ? make_float2(xv[r].z, xv[r].w) : make_float2(xv[r].x, xv[r].y);
@@ -108,73 +143,142 @@ __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float
   }
 }
 
+#ifdef HTR_GEMV_TRACE
+// timeline probe for experiments: per-CTA %globaltimer stamps, compiled only on request
+static __device__ unsigned long long htr_trace_buf[2048 * 8];
+__device__ __forceinline__ void trace_stamp(int slot) {
+  if (threadIdx.x == 0 && blockIdx.x < 2048) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    htr_trace_buf[blockIdx.x * 8 + slot] = t;
+  }
+}
+#define HTR_TRACE(slot) trace_stamp(slot)
+#else
+#define HTR_TRACE(slot)
+#endif
+
 template <int K, int MT>
 __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvParams p) {
-  // staged activations during the sweep; reused for the cross-warp reduction at the end of a row block
-  __shared__ __align__(16) float smem[MT * kStageCols];
+  extern __shared__ __align__(128) unsigned char dyn_smem[];
+  float* smem = reinterpret_cast<float*>(dyn_smem);                               // [MT][kStageCols], later reductions
+  uint32_t* ring = reinterpret_cast<uint32_t*>(dyn_smem + MT * kStageCols * 4);   // [kRing][warps][4 tiles][8K]
   __shared__ int s_arrival;
 
+  HTR_TRACE(0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = warp & 1, c = warp >> 1, g = lane >> 3, q = lane & 7;
-  const long long U = p.units, G = gridDim.x;
-  const long long u_begin = (long long)blockIdx.x * U / G, u_end = ((long long)blockIdx.x + 1) * U / G;
-  const int CG = p.cg, nt = p.nt, n = nt * 16, m = p.mt * 16;
-  const int hist_lane = (lane & ~7) | ((q + 7) & 7);
+  const int U = p.units, G = gridDim.x, CG = p.cg, nt = p.nt, n = nt * 16, m = p.mt * 16;
+  int u_begin, u_end;
+  if (p.split > 0) {
+    const int brb = blockIdx.x / p.split, part = blockIdx.x - brb * p.split;
+    u_begin = brb * CG + part * CG / p.split;
+    u_end = brb * CG + (part + 1) * CG / p.split;
+  } else {
+    u_begin = (int)((long long)blockIdx.x * U / G);
+    u_end = (int)(((long long)blockIdx.x + 1) * U / G);
+  }
+  constexpr int kTileWords = 8 * K, kTileBytes = 32 * K, kTileChunks = 2 * K;    // 16-byte chunks per tile
+  constexpr int kStageBytes = kGemvWarps * 4 * kTileBytes;
 
-  auto unit_ptr = [&](long long u) -> const uint32_t* {
-    const int rb = (int)(u / CG), cgi = (int)(u - (long long)rb * CG);
-    const size_t tile = (size_t)(rb * 8 + 4 * h + g) * nt + (size_t)(4 * cgi + c);
-    return p.qw + tile * (8 * K) + q * K;
+  // ring slot of (this warp, strip g): a lane group of 8 copies and reads its own tile
+  const uint32_t* my_ring = ring + (warp * 4 + g) * kTileWords;
+  const uint32_t ring_dst = (uint32_t)__cvta_generic_to_shared(my_ring) + q * 16;
+
+  int rb = u_begin / CG, cgi = u_begin - rb * CG;
+
+  // prefetch cursor: runs kRing units ahead of the consumer along the same unit sequence.  Offsets are kept in
+  // 16-byte units relative to this lane's first chunk, so the bookkeeping is 32-bit.
+  const char* lane_base = reinterpret_cast<const char*>(p.qw) + ((size_t)(rb * 8 + 4 * h + g) * nt + (size_t)(4 * cgi + c)) * kTileBytes + q * 16;
+  constexpr int kStep16 = 4 * kTileBytes / 16;                    // next column group: four tiles further along the strip
+  const int wrap_extra16 = (7 * nt + 4) * (kTileBytes / 16) - kStep16;   // ... or the first column group of the next row block
+  int pf_off16 = 0, pf_left = u_end - u_begin, pf_in_rb = CG - cgi;
+  auto issue = [&](int stage_bytes) {
+    if (pf_left > 0) {
+      const char* src = lane_base + (size_t)(unsigned)pf_off16 * 16;
+#pragma unroll
+      for (int j = 0; j < (kTileChunks + 7) / 8; ++j)
+        if (8 * j + 8 <= kTileChunks || q + 8 * j < kTileChunks) async_copy16(ring_dst + stage_bytes + j * 128, src + j * 128);
+      --pf_left;
+      pf_off16 += kStep16;
+      if (--pf_in_rb == 0) {
+        pf_off16 += wrap_extra16;
+        pf_in_rb = CG;
+      }
+    }
+    async_commit();
   };
-
-  uint32_t next[K];
-  if (u_begin < u_end) load_unit_words<K>(unit_ptr(u_begin), next);
+  issue(0);
+  // everything above touched only the weights; what follows reads activations and writes shared state
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  bool predecessor_done = false;
+  if (!p.independent) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    predecessor_done = true;
+  }
+  bool ring_primed = false;                        // stages 1.. are issued behind the first activation loads
 
   float2 acc[MT][2];
 #pragma unroll
   for (int r = 0; r < MT; ++r) acc[r][0] = acc[r][1] = make_float2(0.f, 0.f);
 
-  int staged_rb = -1, stage_lo = 0, stage_hi = 0;  // staged tile columns [stage_lo, stage_hi) of row block staged_rb
-
-  for (long long u = u_begin; u < u_end; ++u) {
-    uint32_t V[K + 1];
+  int stage_bytes = 0;
+  int u = u_begin;
+  while (u < u_end) {
+    // ---- segment: units [u, seg_end) lie in row block rb and inside one staged window of activations
+    const int hb0 = cgi >> 1;                                       // first 128-column block needed
+    const int cg_stop = min(CG, cgi + (u_end - u));                 // this CTA's last column group in rb, exclusive
+    const int hb1 = min(hb0 + kStageBlocks, (cg_stop + 1) >> 1);
+    const int seg_cg_end = min(cg_stop, hb1 * 2);
+    __syncthreads();                                                // the previous users of the staging buffer are done
+    const int items = MT * (hb1 - hb0);
+    float4 xv_first = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (warp < items && warp / (hb1 - hb0) < p.rows)                // the first item's loads go out before the copy burst
+      xv_first = load_quad(p.x, (size_t)(warp / (hb1 - hb0)) * n + (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.dtype);
+    if (!ring_primed) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) V[k + 1] = next[k];
-    if (u + 1 < u_end) load_unit_words<K>(unit_ptr(u + 1), next);
-    V[0] = __shfl_sync(kFullWarp, V[K], hist_lane);
-
-    const int rb = (int)(u / CG), cgi = (int)(u - (long long)rb * CG);
-    const int tj = 4 * cgi + c;
-
-    if (rb != staged_rb || 4 * cgi >= stage_hi) {
-      // ---- stage the transformed activations of the next kStageBlocks column blocks (CTA-uniform branch)
-      const int hb0 = cgi >> 1;                                   // first 128-column block needed
-      const int cg_stop = (int)min((long long)CG, cgi + (u_end - u));   // this CTA's last column group in rb, exclusive
-      const int hb1 = min(hb0 + kStageBlocks, (cg_stop + 1) >> 1);
-      __syncthreads();
-      for (int item = warp; item < MT * (hb1 - hb0); item += kGemvThreads / 32) {
-        const int r = item / (hb1 - hb0), hb = hb0 + item % (hb1 - hb0);
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        if (r < p.rows) {
-          const float4 xv = load_quad(p.x, (size_t)r * n + hb * 128 + 4 * lane, p.dtype);
-          const unsigned sg = sign_nibble(p.su, hb * 32 + lane);
-          v[0] = flip(xv.x, sg & 1u); v[1] = flip(xv.y, (sg >> 1) & 1u); v[2] = flip(xv.z, (sg >> 2) & 1u); v[3] = flip(xv.w, sg >> 3);
-          wht128(v, lane);
-        }
-        float* dst = smem + r * kStageCols + (hb - hb0) * 128 + (lane >> 2) * 16;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) dst[staged_col<K>(4 * (lane & 3) + k)] = v[k] * kInvSqrt128;
-      }
-      __syncthreads();
-      staged_rb = rb; stage_lo = hb0 * 8; stage_hi = hb1 * 8;
+      for (int sgi = 1; sgi < kRing; ++sgi) issue(sgi * kStageBytes);
+      ring_primed = true;
     }
+    for (int item = warp; item < items; item += kGemvWarps) {
+      const int r = item / (hb1 - hb0), hb = hb0 + item % (hb1 - hb0);
+      float v[4] = {0.f, 0.f, 0.f, 0.f};
+      if (r < p.rows) {
+        const float4 xv = item == warp ? xv_first : load_quad(p.x, (size_t)r * n + hb * 128 + 4 * lane, p.dtype);
+        const unsigned sg = sign_nibble(p.su, hb * 32 + lane);
+        v[0] = flip(xv.x, sg & 1u); v[1] = flip(xv.y, (sg >> 1) & 1u); v[2] = flip(xv.z, (sg >> 2) & 1u); v[3] = flip(xv.w, sg >> 3);
+        wht128(v, lane);
+      }
+      float* dst = smem + r * kStageCols + (hb - hb0) * 128 + (lane >> 2) * 16;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) dst[staged_col<K>(4 * (lane & 3) + k)] = v[k] * kInvSqrt128;
+    }
+    __syncthreads();
+    HTR_TRACE(1);
 
-    unit_fma<K, MT>(V, smem + (tj - stage_lo) * 16, acc);
-
-    const bool block_done = (cgi == CG - 1) || (u + 1 == u_end);
-    if (!block_done) continue;
+    const float* xs = smem + (4 * cgi + c - hb0 * 8) * 16;
+    const int seg_units = seg_cg_end - cgi;
+#pragma unroll 1
+    for (int i = 0; i < seg_units; ++i) {
+      uint32_t V[K + 1];
+      async_wait<kRing - 1>();                       // the oldest copy group (this unit) has landed
+      __syncwarp();
+#ifdef HTR_GEMV_TRACE
+      if (u + i == u_begin) HTR_TRACE(2);
+#endif
+      read_unit_words<K>(reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_ring) + stage_bytes), q, V);
+      __syncwarp();                                  // every lane has read the slot before it is refilled
+      issue(stage_bytes);
+      stage_bytes = (stage_bytes + kStageBytes == kRing * kStageBytes) ? 0 : stage_bytes + kStageBytes;
+      unit_fma<K, MT>(V, xs, acc);
+      xs += 64;
+    }
+    u += seg_units;
+    cgi += seg_units;
+    if (cgi < CG && u < u_end) continue;              // same row block, next staged window
 
     // ---- this CTA's contribution to row block rb is complete: reduce the four column warps
+    HTR_TRACE(3);
     __syncthreads();                                   // everyone is done reading the staged activations
     float* red = smem;                                  // [4][MT][128]
 #pragma unroll
@@ -184,28 +288,56 @@ __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvPar
         red[(c * MT + r) * 128 + h * 64 + g * 16 + 2 * q + rr] = acc[r][rr].x + acc[r][rr].y;
         acc[r][rr] = make_float2(0.f, 0.f);
       }
-    staged_rb = -1;                                     // the staging buffer is clobbered
     __syncthreads();
 
-    const int first = unit_owner((long long)rb * CG, G, U), last = unit_owner((long long)(rb + 1) * CG - 1, G, U);
-    const int contributors = last - first + 1;
-    float* ytil = smem + 4 * MT * 128;                  // [MT][128], disjoint from red (needs MT*kStageCols >= 5*MT*128)
+    int first, contributors;
+    if (p.split > 0) {
+      first = rb * p.split;
+      contributors = p.split;
+    } else {
+      first = unit_owner((long long)rb * CG, G, U);
+      contributors = unit_owner((long long)(rb + 1) * CG - 1, G, U) - first + 1;
+    }
+    float* ytil = smem + 4 * MT * 128;                  // [MT][128], disjoint from red (MT*kStageCols >= 5*MT*128)
+    // operands of the epilogue are fetched now so that their latency hides behind the arrival handshake
+    const int row0 = rb * 128 + 4 * lane;
+    uint2 sc_raw = make_uint2(0u, 0u);
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    unsigned sv_bits = 0;
+    if (warp < p.rows) {
+      sc_raw = __ldg(reinterpret_cast<const uint2*>(p.scales + row0));
+      sv_bits = sign_nibble(p.sv, rb * 32 + lane);
+      if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
+    }
+    if (!predecessor_done) {                           // deferred wait of the independent-input form
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      predecessor_done = true;
+    }
     bool finish = true;
     if (contributors > 1) {
       float* mine = p.part + ((size_t)rb * p.slots + (blockIdx.x - first)) * (MT * 128);
       for (int e = tid; e < MT * 128; e += kGemvThreads)
         __stcg(mine + e, red[e] + red[MT * 128 + e] + red[2 * MT * 128 + e] + red[3 * MT * 128 + e]);
-      __threadfence();
       __syncthreads();
-      if (tid == 0) s_arrival = atomicAdd(p.counters + rb, 1);
+      if (tid == 0) {
+        __threadfence();                               // the partials of the whole CTA (ordered by the barrier) before the arrival
+        s_arrival = atomicAdd(p.counters + rb, 1);
+        __threadfence();
+      }
       __syncthreads();
+      HTR_TRACE(4);
       finish = (s_arrival == contributors - 1);
       if (finish) {
-        __threadfence();
         const float* slot0 = p.part + (size_t)rb * p.slots * (MT * 128);
         for (int e = tid; e < MT * 128; e += kGemvThreads) {
           float sum = 0.f;
-          for (int sl = 0; sl < contributors; ++sl) sum += __ldcg(slot0 + (size_t)sl * (MT * 128) + e);
+          for (int base = 0; base < contributors; base += 16) {    // 16 loads in flight, added in slot order
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = base + j < contributors ? __ldcg(slot0 + (size_t)(base + j) * (MT * 128) + e) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum += v[j];
+          }
           ytil[e] = sum;
         }
         if (tid == 0) p.counters[rb] = 0;
@@ -216,24 +348,26 @@ __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvPar
     }
     __syncthreads();
     if (finish && warp < p.rows) {
-      // ---- epilogue of row block rb, one warp per activation row
-      const int r = warp, row0 = rb * 128 + 4 * lane;
-      float v[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) v[k] = ytil[r * 128 + 4 * lane + k] * (__half2float(p.scales[row0 + k]) * p.cb);
+      // ---- epilogue of the row block, one warp per activation row
+      const int r = warp;
+      const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.y));
+      float v[4] = {ytil[r * 128 + 4 * lane] * (s01.x * p.cb), ytil[r * 128 + 4 * lane + 1] * (s01.y * p.cb),
+                    ytil[r * 128 + 4 * lane + 2] * (s23.x * p.cb), ytil[r * 128 + 4 * lane + 3] * (s23.y * p.cb)};
       wht128(v, lane);
-      const unsigned sg = sign_nibble(p.sv, rb * 32 + lane);
-      float4 o = make_float4(flip(v[0] * kInvSqrt128, sg & 1u), flip(v[1] * kInvSqrt128, (sg >> 1) & 1u),
-                             flip(v[2] * kInvSqrt128, (sg >> 2) & 1u), flip(v[3] * kInvSqrt128, sg >> 3));
-      if (p.bias) {
-        const float4 b = load_quad(p.bias, row0, p.dtype);
-        o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-      }
+      float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
+                             flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
+      o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
       store_quad(p.y, (size_t)r * m + row0, p.dtype, o);
     }
-    // the next row block restages before it touches smem again (staged_rb == -1 forces the barrier)
+    if (cgi == CG) { cgi = 0; ++rb; }
+    HTR_TRACE(5);
   }
+  async_wait<0>();
+  HTR_TRACE(6);
 }
+
+// HTR_GEMV_OVERLAP=0 in the environment launches without programmatic stream serialisation (for A/B timing)
+bool gemv_overlap_enabled();
 
 // host-side launcher of one instantiation, defined once per K in packed_gemv_k*.cu
 template <int K>

@@ -3,16 +3,42 @@
 
 namespace htr {
 
+// dynamic shared memory beyond 48 KB needs an opt-in, done once per device and instantiation
+template <int K, int MT>
+static int allow_smem() {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < 64 && done[dev]) return 0;
+  e = cudaFuncSetAttribute(packed_gemv_kernel<K, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemv_smem_bytes<K, MT>());
+  if (e != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < 64) done[dev] = true;
+  return 0;
+}
+
 template <int K, int MT>
 static int launch_one(const GemvParams& p, int grid, cudaStream_t stream) {
-  packed_gemv_kernel<K, MT><<<grid, kGemvThreads, 0, stream>>>(p);
-  return (int)cudaGetLastError();
+  if (const int e = allow_smem<K, MT>()) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kGemvThreads);
+  cfg.dynamicSmemBytes = gemv_smem_bytes<K, MT>();
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = gemv_overlap_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, packed_gemv_kernel<K, MT>, p);
 }
 
 template <int K, int MT>
 static int occupancy_one() {
   int ctas = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, packed_gemv_kernel<K, MT>, kGemvThreads, 0) != cudaSuccess) return -1;
+  if (allow_smem<K, MT>()) return -1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, packed_gemv_kernel<K, MT>, kGemvThreads, gemv_smem_bytes<K, MT>()) != cudaSuccess)
+    return -1;
   return ctas;
 }
 
@@ -39,3 +65,11 @@ int packed_gemv_ctas_per_sm<HTR_INST_K>(int mt_rows) {
 }
 
 }  // namespace htr
+
+#ifdef HTR_GEMV_TRACE
+#if HTR_INST_K == 4
+extern "C" int htr_trace_read(unsigned long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, htr::htr_trace_buf, sizeof(unsigned long long) * n);
+}
+#endif
+#endif

@@ -24,6 +24,8 @@ CB = wire.cbscale()
 GEMV_MAX_M = _lib.GEMV_MAX_ROWS
 GEMV_LOOP_MAX = int(os.environ.get("HTR_GEMV_LOOP_MAX", "64"))
 
+_FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
+
 _DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 _WORKSPACES = {}
 _MIN_WORKSPACE = 1 << 22
@@ -73,9 +75,27 @@ def _gemv(x2, qweight, scales, su, sv, bias, out):
         _lib.check(_lib.lib.htr_linear_plan(M, mt * 16, nt * 16, K, None, None), "htr_linear")
     ws = workspace(x2.device, need)
     st = torch.cuda.current_stream(x2.device).cuda_stream
-    rc = _lib.lib.htr_linear(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
-                             sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st)
+    rc = _lib.lib.htr_linear_ex(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
+                                sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st,
+                                _FLAGS)
     _lib.check(rc, "htr_linear")
+
+
+class independent_inputs:
+    """Context manager: inside it, every packed linear promises that its activations, bias and output are not
+    touched by the kernel launched just before it on the stream (e.g. the experts of one MoE layer, or the
+    shards of one activation).  Such launches overlap their predecessor completely (HTR_LINEAR_INPUT_INDEPENDENT)."""
+
+    def __enter__(self):
+        global _FLAGS
+        self._old = _FLAGS
+        _FLAGS = _FLAGS | _lib.INPUT_INDEPENDENT
+        return self
+
+    def __exit__(self, *exc):
+        global _FLAGS
+        _FLAGS = self._old
+        return False
 
 
 def _linear_impl(x2, qweight, scales, su, sv, bias):

@@ -72,6 +72,16 @@ int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int
                const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
                size_t workspace_bytes, htr_stream_t stream);
 
+/* htr_linear with flags.  HTR_LINEAR_INPUT_INDEPENDENT promises that x, bias and y are neither written nor read by
+ * the kernel that precedes this call in the stream; the launch then overlaps that kernel completely and waits for
+ * it only before it touches the shared workspace.  Without the flag the launch still starts early and prefetches
+ * packed words, but waits for its predecessor before reading x.  (No counterpart in the reference, whose
+ * launches serialise on the stream, htr_kernels.cu:920.) */
+#define HTR_LINEAR_INPUT_INDEPENDENT 1u
+int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+                  const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
+                  size_t workspace_bytes, htr_stream_t stream, unsigned flags);
+
 /* Original-basis weight W = Sv Ho Q Hi Su as bf16 / f16 / f32 [m, n] (debug and prefill hook).
  * Stands in for dequant_w (htr_kernels.cpp:13, k_dequant_w* htr_kernels.cu:658-903); compared with
  * wire.dequant (htr/wire.py:105-113). */

@@ -49,7 +49,7 @@ def test_status_codes_without_touching_the_gpu(lib):
     assert L.htr_linear(16, 0, 1, 8, 8, 8, 4, 16, 16, 16, None, 16, None, 0, None) == -6                 # misaligned qweight
     assert L.htr_dequant_w(None, 8, 8, 4, None, None, None, None, 7, None) == -3
     assert b"K" in L.htr_status_string(-1)
-    assert L.htr_linear_counter_bytes(4096) == 256
+    assert L.htr_linear_counter_bytes(4096) == 65536
 
 
 def test_kernel_decode_arithmetic_on_the_host(tmp_path):
