@@ -82,6 +82,18 @@ int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, 
                   const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
                   size_t workspace_bytes, htr_stream_t stream, unsigned flags);
 
+/* htr_linear without a workspace argument, for callers that cannot allocate device memory when they need the
+ * linear (stream capture in progress, allocation-free real-time loops, hosts whose allocator is not theirs to call).
+ * The scratch is a fixed array of HTR_STATIC_WORKSPACE_BYTES inside the library image, held by every GPU that
+ * loads the library until the process exits; sizes whose scratch exceeds it return HTR_ERR_TOO_LARGE.  The first
+ * call on each device resolves the array's device address and clears its counters on `stream`: make that first
+ * call before any stream capture begins.  All calls on a device share the array, so calls that overlap on the GPU
+ * (different streams) race; order them on one stream.  The entry point itself calls no allocating routine.
+ * This entry point has no counterpart in the reference. */
+#define HTR_STATIC_WORKSPACE_BYTES (4u << 20)
+int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+                      const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, htr_stream_t stream);
+
 /* Original-basis weight W = Sv Ho Q Hi Su as bf16 / f16 / f32 [m, n] (debug and prefill hook).
  * Stands in for dequant_w (htr_kernels.cpp:13, k_dequant_w* htr_kernels.cu:658-903); compared with
  * wire.dequant (htr/wire.py:105-113). */
