@@ -7,7 +7,7 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libhtr_b200.so")
+LIB_PATH = os.environ.get("HTR_B200_LIB") or os.path.join(_HERE, "libhtr_b200.so")   # HTR_B200_LIB: alternative build
 
 BF16, F16, F32 = 0, 1, 2
 GEMV_MAX_ROWS = 8

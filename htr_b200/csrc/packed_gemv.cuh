@@ -20,7 +20,7 @@
 //
 // Inside a CTA (256 threads): warp = (half h of the row block: strips 4h..4h+3) x (tile column c of the
 // unit); lane = (strip g, row pair q).  The packed words travel global -> shared memory through a ring of
-// kRing asynchronous copy stages per warp (16-byte cp.async, several units in flight per warp, no
+// kRing slots per warp, kRing - 1 of them in flight (16-byte cp.async, several units in flight per warp, no
 // registers held while they fly); a lane then reads its K words and the history word, rebuilds 32
 // codebook integers in registers and multiplies them with the transformed activations, which all lanes of
 // the warp read from shared memory at the same address (broadcast).
@@ -31,6 +31,18 @@
 // scalar ones), and part of the byte sums are moved to the shift/logic pipe (see unit_fma).
 #pragma once
 #include "htr_codec.cuh"
+
+// build-time tuning knobs (defaults are the measured best)
+#ifndef HTR_GEMV_ALU4
+#define HTR_GEMV_ALU4 3
+#endif
+#ifndef HTR_GEMV_UNROLL
+#define HTR_GEMV_UNROLL 1
+#endif
+#ifndef HTR_GEMV_RING
+#define HTR_GEMV_RING 5
+#endif
+
 #include "htr_common.cuh"
 
 namespace htr {
@@ -39,7 +51,9 @@ constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kStageBlocks = 8;                  // 128-column blocks of activations staged at a time
 constexpr int kStageCols = kStageBlocks * 128;   // 1024 activations per row
-constexpr int kRing = 4;                         // asynchronous copy stages per warp
+constexpr int kLoopUnroll = HTR_GEMV_UNROLL;                   // unit loop unrolling
+constexpr int kRing = HTR_GEMV_RING;                         // ring slots per warp; kRing - 1 units are in flight
+constexpr int kDepth = kRing - 1;
 constexpr int kCounterBytes = 1 << 16;           // arrival counters at the start of the workspace (16384 row blocks)
 
 struct GemvParams {
@@ -72,6 +86,13 @@ constexpr int gemv_smem_bytes() { return MT * kStageCols * 4 + kRing * kGemvWarp
 
 __device__ __forceinline__ void async_copy16(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+// the same copy, performed only when `on` is non-zero (a predicated instruction: no branch, no reconvergence point)
+__device__ __forceinline__ void async_copy16_if(uint32_t smem_addr, const void* gptr, int on) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0], [%1], 16;\n\t}" ::"r"(smem_addr),
+      "l"(gptr), "r"(on)
+      : "memory");
 }
 __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int PENDING>
@@ -115,7 +136,7 @@ __device__ __forceinline__ constexpr int staged_col_inv(int pos) {
 // Pipe balance (measured on B200 with issue-rate probes): the hash multiply-add, the byte dot product and
 // the packed float ops share one half-rate pipe, the shifts/masks and the byte-wise |a-b| sum share another.
 // ALU4 of every 4 byte sums therefore go through the |a-b| form so that both pipes fill up together.
-template <int K, int MT, int ALU4 = 3>
+template <int K, int MT, int ALU4 = HTR_GEMV_ALU4>
 __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float* __restrict__ xs, float2 (&acc)[MT][2]) {
   uint32_t s[32];
   unit_states<K>(V, s);
@@ -132,7 +153,11 @@ __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float
       for (int rr = 0; rr < 2; ++rr) {
         const uint32_t b0 = (2 * half + 2 * rr) % 4 < ALU4 ? code_magic_bits_alu(s[rr * 16 + c0]) : code_magic_bits(s[rr * 16 + c0]);
         const uint32_t b1 = (2 * half + 2 * rr + 1) % 4 < ALU4 ? code_magic_bits_alu(s[rr * 16 + c1]) : code_magic_bits(s[rr * 16 + c1]);
+#ifdef HTR_GEMV_SCALAR_UNBIAS
+        const float2 w = make_float2(__uint_as_float(b0) - kMagic, __uint_as_float(b1) - kMagic);
+#else
         const float2 w = __fadd2_rn(make_float2(__uint_as_float(b0), __uint_as_float(b1)), unbias);
+#endif
 #pragma unroll
         for (int r = 0; r < MT; ++r) {
           const float2 xp = half ? make_float2(xv[r].z, xv[r].w) : make_float2(xv[r].x, xv[r].y);
@@ -159,7 +184,7 @@ __device__ __forceinline__ void trace_stamp(int slot) {
 #endif
 
 template <int K, int MT>
-__global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1)) packed_gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   float* smem = reinterpret_cast<float*>(dyn_smem);                               // [MT][kStageCols], later reductions
   uint32_t* ring = reinterpret_cast<uint32_t*>(dyn_smem + MT * kStageCols * 4);   // [kRing][warps][4 tiles][8K]
@@ -194,17 +219,19 @@ __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvPar
   const int wrap_extra16 = (7 * nt + 4) * (kTileBytes / 16) - kStep16;   // ... or the first column group of the next row block
   int pf_off16 = 0, pf_left = u_end - u_begin, pf_in_rb = CG - cgi;
   auto issue = [&](int stage_bytes) {
-    if (pf_left > 0) {
-      const char* src = lane_base + (size_t)(unsigned)pf_off16 * 16;
+    // branch-free: past the end of the range the copies are predicated off and the cursor runs on harmlessly
+    const int on = pf_left > 0;
+    const char* src = lane_base + (size_t)(unsigned)pf_off16 * 16;
 #pragma unroll
-      for (int j = 0; j < (kTileChunks + 7) / 8; ++j)
-        if (8 * j + 8 <= kTileChunks || q + 8 * j < kTileChunks) async_copy16(ring_dst + stage_bytes + j * 128, src + j * 128);
-      --pf_left;
-      pf_off16 += kStep16;
-      if (--pf_in_rb == 0) {
-        pf_off16 += wrap_extra16;
-        pf_in_rb = CG;
-      }
+    for (int j = 0; j < (kTileChunks + 7) / 8; ++j) {
+      if (8 * j + 8 <= kTileChunks) async_copy16_if(ring_dst + stage_bytes + j * 128, src + j * 128, on);
+      else async_copy16_if(ring_dst + stage_bytes + j * 128, src + j * 128, on && (q + 8 * j < kTileChunks));
+    }
+    --pf_left;
+    pf_off16 += kStep16;
+    if (--pf_in_rb == 0) {
+      pf_off16 += wrap_extra16;
+      pf_in_rb = CG;
     }
     async_commit();
   };
@@ -222,7 +249,7 @@ __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvPar
 #pragma unroll
   for (int r = 0; r < MT; ++r) acc[r][0] = acc[r][1] = make_float2(0.f, 0.f);
 
-  int stage_bytes = 0;
+  int stage_bytes = 0, refill_bytes = (kRing - 1) * kStageBytes;
   int u = u_begin;
   while (u < u_end) {
     // ---- segment: units [u, seg_end) lie in row block rb and inside one staged window of activations
@@ -237,7 +264,7 @@ __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvPar
       xv_first = load_quad(p.x, (size_t)(warp / (hb1 - hb0)) * n + (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.dtype);
     if (!ring_primed) {
 #pragma unroll
-      for (int sgi = 1; sgi < kRing; ++sgi) issue(sgi * kStageBytes);
+      for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
       ring_primed = true;
     }
     for (int item = warp; item < items; item += kGemvWarps) {
@@ -258,17 +285,17 @@ __global__ void __launch_bounds__(kGemvThreads) packed_gemv_kernel(const GemvPar
 
     const float* xs = smem + (4 * cgi + c - hb0 * 8) * 16;
     const int seg_units = seg_cg_end - cgi;
-#pragma unroll 1
+#pragma unroll kLoopUnroll
     for (int i = 0; i < seg_units; ++i) {
       uint32_t V[K + 1];
-      async_wait<kRing - 1>();                       // the oldest copy group (this unit) has landed
-      __syncwarp();
+      async_wait<kDepth - 1>();                      // the oldest copy group (this unit) has landed
+      __syncwarp();                                  // ... for every lane; and every lane is done with the previous slot
 #ifdef HTR_GEMV_TRACE
       if (u + i == u_begin) HTR_TRACE(2);
 #endif
       read_unit_words<K>(reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_ring) + stage_bytes), q, V);
-      __syncwarp();                                  // every lane has read the slot before it is refilled
-      issue(stage_bytes);
+      issue(refill_bytes);                           // refill the slot that was consumed one unit ago (or never used yet)
+      refill_bytes = stage_bytes;
       stage_bytes = (stage_bytes + kStageBytes == kRing * kStageBytes) ? 0 : stage_bytes + kStageBytes;
       unit_fma<K, MT>(V, xs, acc);
       xs += 64;

@@ -28,6 +28,7 @@ _FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of thi
 
 _DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 _WORKSPACES = {}
+_NEED = {}
 _MIN_WORKSPACE = 1 << 22
 
 
@@ -70,9 +71,13 @@ def _gemv(x2, qweight, scales, su, sv, bias, out):
     M = x2.shape[0]
     mt, nt, W = qweight.shape
     K = W // 8
-    need = _lib.lib.htr_linear_workspace_bytes(M, mt * 16, nt * 16, K)
-    if need == 0:
-        _lib.check(_lib.lib.htr_linear_plan(M, mt * 16, nt * 16, K, None, None), "htr_linear")
+    key = (x2.device.index, M, mt, nt, K)
+    need = _NEED.get(key)
+    if need is None:
+        need = _lib.lib.htr_linear_workspace_bytes(M, mt * 16, nt * 16, K)
+        if need == 0:
+            _lib.check(_lib.lib.htr_linear_plan(M, mt * 16, nt * 16, K, None, None), "htr_linear")
+        _NEED[key] = need
     ws = workspace(x2.device, need)
     st = torch.cuda.current_stream(x2.device).cuda_stream
     rc = _lib.lib.htr_linear_ex(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
@@ -131,5 +136,9 @@ def _(x2, qweight, scales, su, sv, bias):
 def linear(x, qweight, scales, su, sv, bias=None):
     """y = x @ W^T (+ bias) for an HTR-W1 weight; x [..., n] -> [..., m] in x.dtype (htr/ops.py:118-122)."""
     lead = x.shape[:-1]
-    y = htr_linear_op(x.reshape(-1, x.shape[-1]), qweight, scales, su, sv, bias)
+    x2 = x.reshape(-1, x.shape[-1])
+    if torch.compiler.is_compiling():
+        y = htr_linear_op(x2, qweight, scales, su, sv, bias)      # traced programs see the registered op
+    else:
+        y = _linear_impl(x2.contiguous(), qweight, scales, su, sv, bias)   # eager: skip the dispatcher round trip
     return y.reshape(*lead, qweight.shape[0] * 16)
