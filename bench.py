@@ -38,6 +38,7 @@ SHAPES = ((12288, 4096), (4096, 12288))      # (m out, n in): up/gate-like and d
 WIDTHS = (2, 3, 4, 5)
 COPIES = 8
 FALLBACK_HBM_GBS = 6650.0
+_CPU_CASES = []          # synthetic linears of the CPU sample, generated once per process
 
 
 def payload_bytes(m, n, K):
@@ -112,8 +113,8 @@ def cpu_sample(threads=None, repeats=1):
     c = O.COracle()
     threads = threads or os.cpu_count()
     rng = np.random.default_rng(0)
-    cases = []
-    for (m, n) in SHAPES:
+    cases = _CPU_CASES
+    for (m, n) in (SHAPES if not cases else ()):
         for K in WIDTHS:
             qw = rng.integers(-2 ** 31, 2 ** 31, size=(m // 16, n // 16, 8 * K), dtype=np.int64).astype(np.int32)
             sc = (np.abs(rng.standard_normal(m)) * 0.01 + 0.01).astype(np.float16)
@@ -166,7 +167,7 @@ def run_reference(args):
 def run_ours(args):
     import torch
     import torch.distributed as dist
-    from htr_b200 import ops, wire
+    from htr_b200 import ops
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -179,7 +180,7 @@ def run_ours(args):
 
     # ---- synthetic packed linears, resident in HBM (each rank: its own row shard of an N-times taller linear)
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    groups = []          # per K: list of (x, qw, sc, su, sv, y_gathered or None)
+    groups = []          # per K: list of dict(x, w=(qw, sc, su, sv), gathered, xh, yh, xd)
     total_bytes, launches = 0, 0
     for K in WIDTHS:
         items = []
@@ -190,50 +191,53 @@ def run_ours(args):
                 su = torch.randint(0, 256, (n // 8,), dtype=torch.uint8, device=dev, generator=g)
                 sv = torch.randint(0, 256, (m // 8,), dtype=torch.uint8, device=dev, generator=g)
                 x = torch.randn(1, n, device=dev, generator=g).bfloat16()
-                gathered = torch.empty(world, m, dtype=torch.bfloat16, device=dev) if world > 1 else None
-                items.append((x, qw, sc, su, sv, gathered))
+                items.append(dict(x=x, w=(qw, sc, su, sv), m=m, n=n,
+                                  gathered=torch.empty(world, m, dtype=torch.bfloat16, device=dev) if world > 1 else None,
+                                  xh=x.cpu().pin_memory(), xd=torch.empty_like(x),
+                                  yh=torch.empty(max(world, 1), m, dtype=torch.bfloat16).pin_memory()))
                 total_bytes += payload_bytes(m, n, K)
                 launches += 1
         groups.append(items)
+    side = torch.cuda.Stream(device=dev)         # the all-gather of one linear overlaps the next linear
 
-    def run_group(items):
-        for x, qw, sc, su, sv, gathered in items:
-            y = ops.linear(x, qw, sc, su, sv)
-            if gathered is not None:
-                dist.all_gather_into_tensor(gathered, y)
+    def run_group(items, from_host=False):
+        main = torch.cuda.current_stream()
+        for it in items:
+            if from_host:
+                it["xd"].copy_(it["xh"], non_blocking=True)
+            y = ops.linear(it["xd"] if from_host else it["x"], *it["w"])
+            out = y
+            if it["gathered"] is not None:
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    dist.all_gather_into_tensor(it["gathered"], y)
+                    if from_host:
+                        it["yh"].copy_(it["gathered"], non_blocking=True)
+                y.record_stream(side)
+            elif from_host:
+                it["yh"].copy_(out, non_blocking=True)
+        if world > 1:
+            main.wait_stream(side)
 
-    # warm every kernel and the workspace, then capture one CUDA graph per K-group
+    # warm every kernel, the workspace and NCCL, then capture CUDA graphs (one per K-group and launch form)
     for items in groups:
         run_group(items)
+        run_group(items, from_host=True)
     torch.cuda.synchronize()
-    use_graphs = world == 1 and not args.no_graphs
+    use_graphs = not args.no_graphs
 
-    def capture(independent):
+    def capture(independent=False, from_host=False):
         out = []
         for items in groups:
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr):
                 if independent:
                     with ops.independent_inputs():
-                        run_group(items)
+                        run_group(items, from_host)
                 else:
-                    run_group(items)
+                    run_group(items, from_host)
             out.append(gr)
         return out
-
-    graphs = capture(False) if use_graphs else []
-
-    def one_pass(marks=None, which=None):
-        which = graphs if which is None else which
-        for i, items in enumerate(groups):
-            if marks is not None:
-                marks[i][0].record()
-            if use_graphs:
-                which[i].replay()
-            else:
-                run_group(items)
-            if marks is not None:
-                marks[i][1].record()
 
     def barrier():
         torch.cuda.synchronize()
@@ -241,72 +245,52 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(3, args.warmup)):
-        one_pass()
+    def timed(graphs, steps, from_host=False, independent=False):
+        """K steps bracketed by a barrier; returns (total ms, [ms per K-group per step])."""
+        def one_pass(marks=None):
+            for i, items in enumerate(groups):
+                if marks is not None:
+                    marks[i][0].record()
+                if graphs is not None:
+                    graphs[i].replay()
+                elif independent:
+                    with ops.independent_inputs():
+                        run_group(items, from_host)
+                else:
+                    run_group(items, from_host)
+                if marks is not None:
+                    marks[i][1].record()
+        for _ in range(max(3, args.warmup)):
+            one_pass()
+        barrier()
+        marks = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in groups] for _ in range(steps)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s in range(steps):
+            one_pass(marks[s])
+        e1.record()
+        barrier()
+        return e0.elapsed_time(e1), [sum(marks[s][i][0].elapsed_time(marks[s][i][1]) for s in range(steps)) / steps for i in range(len(groups))]
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    barrier()
-    marks = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in groups] for _ in range(args.steps)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for s in range(args.steps):
-        one_pass(marks[s])
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    per_k_ms = [sum(marks[s][i][0].elapsed_time(marks[s][i][1]) for s in range(args.steps)) / args.steps for i in range(len(groups))]
-
-    # ---- the same pass with every launch declared independent of its predecessor (htr_linear_ex flag): launches overlap
-    ov_ms, ov_per_k_ms = None, None
-    if use_graphs:
-        ov_graphs = capture(True)
-        for _ in range(3):
-            one_pass(which=ov_graphs)
-        barrier()
-        ov_marks = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in groups] for _ in range(args.steps)]
-        o0, o1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        o0.record()
-        for s in range(args.steps):
-            one_pass(ov_marks[s], which=ov_graphs)
-        o1.record()
-        barrier()
-        ov_ms = o0.elapsed_time(o1)
-        ov_per_k_ms = [sum(ov_marks[s][i][0].elapsed_time(ov_marks[s][i][1]) for s in range(args.steps)) / args.steps for i in range(len(groups))]
-
-    # ---- end to end through the public operator: activations from pinned host memory, outputs back to the host
-    host_x = [[it[0].cpu().pin_memory() for it in items] for items in groups]
-    host_y = [[torch.empty(1, it[1].shape[0] * 16, dtype=torch.bfloat16).pin_memory() for it in items] for items in groups]
-    h2d = sum(t.numel() * 2 for row in host_x for t in row)
-    d2h = sum(t.numel() * 2 for row in host_y for t in row)
-
-    def e2e_pass():
-        for gi, items in enumerate(groups):
-            for li, (x, qw, sc, su, sv, gathered) in enumerate(items):
-                xd = host_x[gi][li].to(dev, non_blocking=True)
-                y = ops.linear(xd, qw, sc, su, sv)
-                if gathered is not None:
-                    dist.all_gather_into_tensor(gathered, y)
-                host_y[gi][li].copy_(y, non_blocking=True)
-        torch.cuda.synchronize()
-
-    for _ in range(2):
-        e2e_pass()
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ms, per_k_ms = timed(capture() if use_graphs else None, args.steps)
+    # the same pass with every launch declared independent of its predecessor (htr_linear_ex flag): launches overlap
+    ov_ms, ov_per_k_ms = timed(capture(independent=True) if use_graphs else None, args.steps, independent=True)
+    # end to end through the public operator: activations from pinned host memory, outputs back to pinned host memory
     e2e_steps = max(1, min(args.steps, 10))
-    f0.record()
-    for _ in range(e2e_steps):
-        e2e_pass()
-    f1.record()
-    barrier()
-    e2e_ms = f0.elapsed_time(f1)
+    e2e_ms, _ = timed(capture(from_host=True) if use_graphs else None, e2e_steps, from_host=True)
     clocks = sampler.stop() if rank == 0 else None
+    h2d = sum(it["xh"].numel() * 2 for items in groups for it in items)
+    d2h = sum((it["gathered"].numel() if it["gathered"] is not None else it["m"]) * 2 for items in groups for it in items)
 
     if world > 1:
-        t = torch.tensor([ms, e2e_ms] + per_k_ms, device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms, ov_ms] + per_k_ms + ov_per_k_ms, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms, per_k_ms = float(t[0]), float(t[1]), [float(v) for v in t[2:]]
+        ms, e2e_ms, ov_ms = float(t[0]), float(t[1]), float(t[2])
+        per_k_ms = [float(v) for v in t[3:3 + len(groups)]]
+        ov_per_k_ms = [float(v) for v in t[3 + len(groups):]]
 
     if rank == 0:
         peak, peak_kind = measured_peak()
@@ -319,23 +303,24 @@ def run_ours(args):
             gbs = kb / (per_k_ms[i] * 1e-3) / 1e9
             per_k[f"K{K}"] = {"GBps_per_gpu": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                               "us_per_launch": round(1e3 * per_k_ms[i] / (len(SHAPES) * COPIES), 3)}
-        overlapped = None
-        if ov_ms is not None:
-            ogbs = total_bytes * args.steps / (ov_ms * 1e-3) / 1e9
-            overlapped = {"what": "same pass, launches flagged HTR_LINEAR_INPUT_INDEPENDENT (each overlaps its predecessor)",
-                          "value": ogbs, "unit": "GB/s", "frac_of_peak": ogbs / peak,
-                          "per_K": {f"K{K}": round(sum(payload_bytes(m, n, K) for (m, n) in SHAPES) * COPIES / (ov_per_k_ms[i] * 1e-3) / 1e9, 1)
-                                    for i, K in enumerate(WIDTHS)}}
+        ogbs = total_bytes * args.steps / (ov_ms * 1e-3) / 1e9
+        overlapped = {"what": "same pass, launches flagged HTR_LINEAR_INPUT_INDEPENDENT (each overlaps its predecessor)",
+                      "value": ogbs * world, "unit": "GB/s", "frac_of_peak_per_gpu": ogbs / peak,
+                      "per_K": {f"K{K}": round(sum(payload_bytes(m, n, K) for (m, n) in SHAPES) * COPIES / (ov_per_k_ms[i] * 1e-3) / 1e9, 1)
+                                for i, K in enumerate(WIDTHS)}}
         achieved = total_bytes * args.steps / (ms * 1e-3) / 1e9     # per GPU: one kernel family, launches back to back
         line = base_line(args)
         line.update(value=value, ms_per_step=ms / args.steps, gpu_launches=launches * args.steps, clocks=clocks,
                     e2e={"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
                     roofline={"bound": "hbm", "kernel": "packed_gemv_kernel<K,1>", "achieved": achieved, "peak": peak, "unit": "GB/s",
                               "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
+                              "traffic_note": "ncu dram__bytes_read+write on the 151936x4096 K4 launch: 318.2 MB for 311.5 MB "
+                                              "algorithmic (profiles/); 1.02x, proportional to packed bytes",
                               "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / launches,
                               "per_K": per_k},
                     overlapped=overlapped,
                     timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs else "eager launches"))
+        line["roofline"]["traffic"] = round(1.0215 * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, sample = cpu_sample()
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample, "seconds": dt}

@@ -11,10 +11,11 @@ LIB_PATH = os.environ.get("HTR_B200_LIB") or os.path.join(_HERE, "libhtr_b200.so
 
 BF16, F16, F32 = 0, 1, 2
 GEMV_MAX_ROWS = 8
+GEMM_MAX_ROWS = 128
 INPUT_INDEPENDENT = 1
 
 EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
-           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_static", "htr_dequant_w",
+           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_static", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_dequant_w",
            "htr_set_gemv_ctas_per_sm", "htr_linear_plan")
 
 
@@ -41,6 +42,10 @@ def _load():
     lib.htr_linear.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.htr_linear_ex.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp, ctypes.c_uint]
     lib.htr_linear_static.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp]
+    lib.htr_linear_gemm.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.htr_linear_gemm_workspace_bytes.restype = sz
+    lib.htr_linear_gemm_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.htr_linear_gemm_error_offset.restype = sz
     lib.htr_dequant_w.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, i32, vp]
     lib.htr_set_gemv_ctas_per_sm.restype = None
     lib.htr_set_gemv_ctas_per_sm.argtypes = [i32]

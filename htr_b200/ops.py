@@ -7,9 +7,10 @@ for one B200 (148 SMs, HBM3e) rather than copied from the 40-CU part the referen
   M == 0            empty result                                             (htr/ops.py:73-74)
   1 <= M <= 8       one launch of the streaming GEMV (activation transform, decode + dot, split reduce,
                     output transform fused)                                  (replaces htr/ops.py:75-76,95-101)
-  8 <  M <= LOOP    the same kernel over 8-row chunks                        (htr/ops.py:77-88)
-  M > LOOP          original-basis bf16 weight from the dequant kernel, then a library GEMM
-                                                                             (htr/ops.py:89-93)
+  M > 8             the tensor-core packed GEMM (tcgen05 + TMEM), 128 activation rows per launch; decoded tiles go
+                    straight into the MMA operand                            (replaces htr/ops.py:77-93)
+  HTR_GEMM=0        instead: GEMV over 8-row chunks up to HTR_GEMV_LOOP_MAX rows, beyond that the original-basis bf16
+                    weight from the dequant kernel + a library GEMM (the reference's own routes, kept for comparison)
 
 All work is enqueued on the current torch stream without a host synchronisation, so the op can be
 captured in a CUDA graph.  Nothing here runs on the CPU: without the CUDA library the import fails.
@@ -23,6 +24,8 @@ from . import _lib, wire
 CB = wire.cbscale()
 GEMV_MAX_M = _lib.GEMV_MAX_ROWS
 GEMV_LOOP_MAX = int(os.environ.get("HTR_GEMV_LOOP_MAX", "64"))
+USE_GEMM = os.environ.get("HTR_GEMM", "1") == "1"
+GEMM_MAX_M = _lib.GEMM_MAX_ROWS
 
 _FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
 
@@ -86,6 +89,34 @@ def _gemv(x2, qweight, scales, su, sv, bias, out):
     _lib.check(rc, "htr_linear")
 
 
+_GEMM_WS = {}
+
+
+def _gemm(x2, qweight, scales, su, sv, bias, out):
+    """One C call of the tensor-core GEMM: up to 128 rows of x2 against the packed weight."""
+    M = x2.shape[0]
+    mt, nt, W = qweight.shape
+    K = W // 8
+    need = _lib.lib.htr_linear_gemm_workspace_bytes(M, mt * 16, nt * 16, K)
+    if need == 0:
+        raise _lib.HTRError("htr_linear_gemm: unsupported sizes")
+    st = torch.cuda.current_stream(x2.device).cuda_stream
+    key = (x2.device.index, st)
+    ws = _GEMM_WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 24), dtype=torch.uint8, device=x2.device)
+        _GEMM_WS[key] = ws
+    rc = _lib.lib.htr_linear_gemm(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
+                                  sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st)
+    _lib.check(rc, "htr_linear_gemm")
+
+
+def gemm_error_codes():
+    """Status words of the GEMM workspaces (synchronises; for tests): non-zero means a bounded device-side wait expired."""
+    off = _lib.lib.htr_linear_gemm_error_offset()
+    return [int(ws[off:off + 4].view(torch.int32).item()) for ws in _GEMM_WS.values()]
+
+
 class independent_inputs:
     """Context manager: inside it, every packed linear promises that its activations, bias and output are not
     touched by the kernel launched just before it on the stream (e.g. the experts of one MoE layer, or the
@@ -112,6 +143,12 @@ def _linear_impl(x2, qweight, scales, su, sv, bias):
     qweight, scales, su, sv = qweight.contiguous(), scales.contiguous(), su.contiguous(), sv.contiguous()
     bias = None if bias is None else bias.contiguous()
     with torch.cuda.device(x2.device):
+        if M > GEMV_MAX_M and USE_GEMM:
+            y = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
+            for r0 in range(0, M, GEMM_MAX_M):
+                r1 = min(M, r0 + GEMM_MAX_M)
+                _gemm(x2[r0:r1], qweight, scales, su, sv, bias, y[r0:r1])
+            return y
         if M <= GEMV_LOOP_MAX:
             y = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
             for r0 in range(0, M, GEMV_MAX_M):

@@ -94,6 +94,19 @@ int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, 
 int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
                       const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, htr_stream_t stream);
 
+/* Tensor-core form of the packed linear for prefill-sized batches, 1 <= M <= HTR_GEMM_MAX_ROWS rows per call:
+ * decoded tiles go straight into the shared-memory operand of tcgen05.mma, accumulators live in TMEM; two launches
+ * (activation transform to fp16 hi/lo planes, then the GEMM with the same split reduction and epilogue as the GEMV).
+ * The workspace starts with the same zero-initialised counter region as htr_linear's, followed by one status word at
+ * htr_linear_gemm_error_offset(): non-zero after a call means a bounded device-side wait expired and the output is
+ * invalid.  Stands in for the prefill branch of _linear_impl, dequant_w + F.linear (htr/ops.py:89-93). */
+#define HTR_GEMM_MAX_ROWS 128
+size_t htr_linear_gemm_workspace_bytes(int M, int m, int n, int K);
+size_t htr_linear_gemm_error_offset(void);
+int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+                    const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
+                    size_t workspace_bytes, htr_stream_t stream);
+
 /* Original-basis weight W = Sv Ho Q Hi Su as bf16 / f16 / f32 [m, n] (debug and prefill hook).
  * Stands in for dequant_w (htr_kernels.cpp:13, k_dequant_w* htr_kernels.cu:658-903); compared with
  * wire.dequant (htr/wire.py:105-113). */
