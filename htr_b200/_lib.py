@@ -12,10 +12,11 @@ LIB_PATH = os.environ.get("HTR_B200_LIB") or os.path.join(_HERE, "libhtr_b200.so
 BF16, F16, F32 = 0, 1, 2
 GEMV_MAX_ROWS = 8
 GEMM_MAX_ROWS = 128
+GEMM_MAX_ROWS_F32 = 64
 INPUT_INDEPENDENT = 1
 
 EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
-           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_static", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_dequant_w",
+           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_static", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_linear_gemm_last_cuda_error", "htr_dequant_w",
            "htr_set_gemv_ctas_per_sm", "htr_linear_plan")
 
 

@@ -8,7 +8,8 @@ namespace htr {
 // ------------------------------------------------------------------------------------------------
 // Activation transform for the GEMM: xt = H128(su * x) / sqrt(128) / tok as two fp16 planes, their row sum, tok.
 // One CTA per activation row (rows beyond `rows` are written as zeros so that the padded batch is harmless).
-__global__ void __launch_bounds__(256) rht_f16_kernel(const void* __restrict__ x, int dtype, int rows, int n, const uint8_t* __restrict__ su,
+__global__ void __launch_bounds__(256) rht_f16_kernel(const void* __restrict__ x, int dtype, int rows, int n, int planes,
+                                                      const uint8_t* __restrict__ su,
                                                       __half* __restrict__ xh, __half* __restrict__ xl, float* __restrict__ xsum,
                                                       float* __restrict__ tok) {
   __shared__ float red[8];
@@ -54,7 +55,7 @@ __global__ void __launch_bounds__(256) rht_f16_kernel(const void* __restrict__ x
       const float t = v[k] * inv;
       hi[k] = __float2half_rn(t);
       lo[k] = __float2half_rn(t - __half2float(hi[k]));
-      sum += __half2float(hi[k]) + __half2float(lo[k]);
+      sum += planes == 2 ? __half2float(hi[k]) + __half2float(lo[k]) : __half2float(hi[k]);   // exactly what the MMA will see
     }
     *reinterpret_cast<uint2*>(xh + at) = *reinterpret_cast<const uint2*>(hi);
     *reinterpret_cast<uint2*>(xl + at) = *reinterpret_cast<const uint2*>(lo);
@@ -71,14 +72,15 @@ __global__ void __launch_bounds__(256) rht_f16_kernel(const void* __restrict__ x
   }
 }
 
-int run_rht_f16(const void* x, int dtype, int rows, int np, int n, const uint8_t* su, __half* xh, __half* xl, float* xsum, float* tok,
-                cudaStream_t st) {
-  rht_f16_kernel<<<np, 256, 0, st>>>(x, dtype, rows, n, su, xh, xl, xsum, tok);
+int run_rht_f16(const void* x, int dtype, int rows, int np, int n, int planes, const uint8_t* su, __half* xh, __half* xl, float* xsum,
+                float* tok, cudaStream_t st) {
+  rht_f16_kernel<<<np, 256, 0, st>>>(x, dtype, rows, n, planes, su, xh, xl, xsum, tok);
   return (int)cudaGetLastError();
 }
 
 namespace {
 
+thread_local int t_gemm_cuda = 0;
 constexpr size_t kCounterRegion = 1 << 16;   // same fixed counter region as the GEMV workspace
 constexpr size_t kErrorRegion = 256;
 
@@ -103,7 +105,7 @@ double codebook_scale() {
   return value;
 }
 
-int make_gemm_plan(int M, int m, int n, GemmPlan* out) {
+int make_gemm_plan(int M, int m, int n, int K, int planes, GemmPlan* out) {
   int dev = 0, sms = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return HTR_ERR_CUDA;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return HTR_ERR_CUDA;
@@ -111,7 +113,10 @@ int make_gemm_plan(int M, int m, int n, GemmPlan* out) {
   g.np = (M + 15) / 16 * 16;
   g.rbs = m / 128;
   g.hb = n / 128;
-  const int per_sm = g.np <= 64 ? 2 : 1;                 // bounded by shared memory (66 KB / 100 KB per CTA) and TMEM columns
+  int per_sm = (227 * 1024) / (gemm_smem_bytes(g.np, planes, K) + 1024);   // bounded by shared memory ...
+  if (per_sm > 3) per_sm = 3;
+  if (per_sm * 2 * g.np > 512) per_sm = 512 / (2 * g.np);                   // ... and by the 512 TMEM columns of an SM
+  if (per_sm < 1) per_sm = 1;
   long long s = (long long)sms * per_sm / g.rbs;
   if (s < 1) s = 1;
   if (s > g.hb) s = g.hb;
@@ -137,9 +142,9 @@ extern "C" {
 
 size_t htr_linear_gemm_workspace_bytes(int M, int m, int n, int K) {
   if (!width_ok(K) || M < 1 || M > HTR_GEMM_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return 0;
-  GemmPlan g;
-  if (make_gemm_plan(M, m, n, &g) != HTR_OK) return 0;
-  return g.total;
+  GemmPlan g1, g2;      // the scratch of either activation form (one or two fp16 planes) must fit
+  if (make_gemm_plan(M, m, n, K, 1, &g1) != HTR_OK || make_gemm_plan(M > HTR_GEMM_MAX_ROWS_F32 ? HTR_GEMM_MAX_ROWS_F32 : M, m, n, K, 2, &g2) != HTR_OK) return 0;
+  return g1.total > g2.total ? g1.total : g2.total;
 }
 
 int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
@@ -154,7 +159,9 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
   if (!a16(x) || !a16(qweight) || !a16(y) || (bias && !a16(bias)) || !a16(workspace) || !a16(scales)) return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
   GemmPlan g;
-  const int rc = make_gemm_plan(M, m, n, &g);
+  const int planes = dtype == HTR_DTYPE_F32 ? 2 : 1;      // 16-bit activations need no lo plane
+  if (planes == 2 && M > HTR_GEMM_MAX_ROWS_F32) return HTR_ERR_BAD_SHAPE;
+  const int rc = make_gemm_plan(M, m, n, K, planes, &g);
   if (rc != HTR_OK) return rc;
   if (!workspace || workspace_bytes < g.total) return HTR_ERR_WORKSPACE;
   char* ws = static_cast<char*>(workspace);
@@ -174,15 +181,16 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
   p.error = reinterpret_cast<int*>(ws + kCounterRegion);
   p.rows = M;
   p.np = g.np;
+  p.planes = planes;
   p.mt = mt;
   p.nt = nt;
   p.dtype = dtype;
   p.hb = g.hb;
   p.split = g.split;
   p.cb = (float)codebook_scale();
-  int e = run_rht_f16(x, dtype, M, g.np, n, su, reinterpret_cast<__half*>(ws + g.off_xh), reinterpret_cast<__half*>(ws + g.off_xl),
+  int e = run_rht_f16(x, dtype, M, g.np, n, planes, su, reinterpret_cast<__half*>(ws + g.off_xh), reinterpret_cast<__half*>(ws + g.off_xl),
                       reinterpret_cast<float*>(ws + g.off_xsum), reinterpret_cast<float*>(ws + g.off_tok), st);
-  if (e) return HTR_ERR_CUDA;
+  if (e) { t_gemm_cuda = e; return HTR_ERR_CUDA; }
   switch (K) {
     case 2: e = launch_packed_gemm_tc<2>(p, g.grid, st); break;
     case 3: e = launch_packed_gemm_tc<3>(p, g.grid, st); break;
@@ -191,8 +199,11 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
     case 6: e = launch_packed_gemm_tc<6>(p, g.grid, st); break;
     case 8: e = launch_packed_gemm_tc<8>(p, g.grid, st); break;
   }
+  if (e) t_gemm_cuda = e;
   return e ? HTR_ERR_CUDA : HTR_OK;
 }
+
+int htr_linear_gemm_last_cuda_error(void) { return t_gemm_cuda; }
 
 size_t htr_linear_gemm_error_offset(void) { return kCounterRegion; }
 

@@ -31,7 +31,10 @@ constexpr int kChunkK = 64;                                 // k extent of one s
 constexpr int kLbo = 128;                                   // bytes between core matrices adjacent in K
 constexpr int kSbo = (kChunkK / 8) * 128 + 16;              // bytes between 8-row groups (padded: 1040)
 constexpr int kATileBytes = (128 / 8) * kSbo;               // 16640
-constexpr int kGemmStages = 2;
+constexpr int kGemmStages = 2;                              // A tiles: one being read by the tensor core, one being decoded
+constexpr int kAhead = 3;                                   // chunks of packed words and activations in flight (cp.async)
+constexpr int kRawSlots = kAhead + 1;                       // packed-word ring per warp
+constexpr int kBStages = kAhead + 2;                        // activation tiles: + one read by the MMA, + one being decoded against
 constexpr unsigned kSpinLimit = 4000000u;                   // iterations of a try_wait loop before giving up
 
 struct GemmParams {
@@ -42,12 +45,13 @@ struct GemmParams {
   void* y;
   const __half* xh;       // [np][n] hi plane of the transformed activations (rows >= rows are zero)
   const __half* xl;       // [np][n] lo plane
-  const float* xsum;      // [np] sum over k of hi + lo
+  const float* xsum;      // [np] sum over k of the planes in use (hi, or hi + lo)
   const float* tok;       // [np] power-of-two range scale per activation row
   float* part;            // [row blocks][slots][np][128]
   int* counters;          // [row blocks]
   int* error;             // one word: first failure code seen by any CTA (0 = none)
   int rows, np;           // activation rows present / padded to a multiple of 16 (16..128)
+  int planes;             // 1: hi plane only (16-bit activations), 2: hi + lo (float32 activations)
   int mt, nt;
   int dtype;
   int hb;                 // 128-column blocks per row (n / 128) = units per row block
@@ -107,12 +111,17 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// dynamic shared memory: stages of (A tile, B tile) -- later reused for the [np][128] float result of a row block
-__host__ __device__ inline int gemm_b_tile_bytes(int np) { return (2 * np / 8) * kSbo; }
-__host__ __device__ inline int gemm_smem_bytes(int np) {
-  const int stages = kGemmStages * (kATileBytes + gemm_b_tile_bytes(np));
+// dynamic shared memory: A tiles, activation tiles, packed-word ring -- later reused for the [np][128] float result
+__host__ __device__ inline int gemm_b_tile_bytes(int ncols) { return (ncols / 8) * kSbo; }
+__host__ __device__ inline int gemm_raw_bytes(int K) { return kRawSlots * kGemmWarps * 4 * 32 * K; }
+__host__ __device__ inline int gemm_smem_bytes(int np, int planes, int K) {
+  const int stages = kGemmStages * kATileBytes + kBStages * gemm_b_tile_bytes(np * planes) + gemm_raw_bytes(K);
   const int result = np * 128 * 4;
   return (stages > result ? stages : result) + 128;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
 template <int K>
@@ -143,13 +152,15 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
   __shared__ int s_arrival, s_fail;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int np = p.np, ncols = 2 * np;                      // accumulator columns: hi plane then lo plane
+  const int np = p.np, ncols = p.planes * np;               // accumulator columns: hi plane, then lo plane if present
   const int nt = p.nt, n = nt * 16, m = p.mt * 16, HB = p.hb;
   const int rb = blockIdx.x / p.split, part_id = blockIdx.x - rb * p.split;
   const int hb_begin = part_id * HB / p.split, hb_end = (part_id + 1) * HB / p.split;
-  const int b_tile_bytes = gemm_b_tile_bytes(np), stage_bytes = kATileBytes + b_tile_bytes;
-  unsigned char* stage0 = gsm + (128 - (smem_u32(gsm) & 127)) % 128;   // 128-byte aligned start
-  const uint32_t stage0_addr = smem_u32(stage0);
+  const int b_tile_bytes = gemm_b_tile_bytes(ncols);
+  unsigned char* stage0 = gsm + (128 - (smem_u32(gsm) & 127)) % 128;   // 128-byte aligned start: A tiles
+  unsigned char* b_stage0 = stage0 + kGemmStages * kATileBytes;        // activation tiles
+  unsigned char* raw0 = b_stage0 + kBStages * b_tile_bytes;            // packed-word ring [slot][warp][4 tiles][8K words]
+  const uint32_t stage0_addr = smem_u32(stage0), b_stage0_addr = smem_u32(b_stage0), raw0_addr = smem_u32(raw0);
 
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < ncols) tmem_cols <<= 1;
@@ -173,31 +184,68 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
 
   // decode role of this thread inside a k-chunk: strip = warp, tile column tc = lane >> 3, row pair q = lane & 7
   const int tc = lane >> 3, q = lane & 7;
-  const int hist_lane = (lane & ~7) | ((q + 7) & 7);
   const size_t strip_tile0 = (size_t)(rb * 8 + warp) * nt;
-
-  uint32_t next[K];
   const int chunks = (hb_end - hb_begin) * 2;                // two 64-column chunks per 128-column block
-  if (chunks > 0) load_lane_words<K>(p.qw + (strip_tile0 + (size_t)hb_begin * 8 + tc) * (8 * K) + q * K, next);
+  constexpr int kWarpRawBytes = 4 * 32 * K, kSlotBytes = kGemmWarps * kWarpRawBytes;
+
+  // asynchronous fetch of chunk c: this warp's four packed tiles (contiguous) and the CTA's activation tile
+  auto prefetch = [&](int c) {
+    if (c < chunks) {
+      const int tile_col0 = hb_begin * 8 + c * 4;
+      const char* wsrc = reinterpret_cast<const char*>(p.qw + (strip_tile0 + tile_col0) * (8 * K));
+      const uint32_t wdst = raw0_addr + (c % kRawSlots) * kSlotBytes + warp * kWarpRawBytes;
+#pragma unroll
+      for (int j = 0; j < (8 * K + 31) / 32; ++j)
+        if (32 * j + 32 <= 8 * K || lane + 32 * j < 8 * K) cp_async16(wdst + (lane + 32 * j) * 16, wsrc + (lane + 32 * j) * 16);
+      const uint32_t bdst = b_stage0_addr + (c % kBStages) * b_tile_bytes;
+      const int k0 = tile_col0 * 16;
+      for (int v = tid; v < ncols * 8; v += kGemmThreads) {
+        const int row = v % ncols, kc = v / ncols;           // row fastest: conflict-free 16-byte stores
+        const __half* src = (row < np ? p.xh + (size_t)row * n : p.xl + (size_t)(row - np) * n) + k0 + kc * 8;
+        cp_async16(bdst + (row >> 3) * kSbo + (row & 7) * 16 + kc * kLbo, src);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+#pragma unroll
+  for (int c = 0; c < kAhead; ++c) prefetch(c);
 
   uint32_t phase_bits = 0u;                                 // bit s = parity of the next completion of stage s's barrier
   bool failed = false;
   for (int ch = 0; ch < chunks; ++ch) {
     const int s = ch & 1;
-    const int tile_col0 = hb_begin * 8 + ch * 4;             // first tile column of this chunk
-    uint32_t V[K + 1];
-#pragma unroll
-    for (int k = 0; k < K; ++k) V[k + 1] = next[k];
-    if (ch + 1 < chunks) load_lane_words<K>(p.qw + (strip_tile0 + tile_col0 + 4 + tc) * (8 * K) + q * K, next);
-    V[0] = __shfl_sync(kFullWarp, V[K], hist_lane);
-
-    // the MMAs that read this stage two chunks ago must have finished (bounded wait, all threads)
+    asm volatile("cp.async.wait_group %0;" ::"n"(kAhead - 1) : "memory");   // this chunk's words and activations have landed
+    // the MMAs that read A stage s (and the activation tile of chunk ch-2) must have finished (bounded wait, all threads)
     if (ch >= kGemmStages && !failed) {
       if (!mbar_wait(smem_u32(&s_bar[s]), (phase_bits >> s) & 1u)) failed = true;
       phase_bits ^= 1u << s;
     }
-    unsigned char* a_tile = stage0 + s * stage_bytes;
-    unsigned char* b_tile = a_tile + kATileBytes;
+    __syncwarp();
+    prefetch(ch + kAhead);                                   // overwrites the activation tile of chunk ch-2 and the word slot of ch-1
+
+    uint32_t V[K + 1];
+    {
+      const uint32_t* tile = reinterpret_cast<const uint32_t*>(raw0 + (ch % kRawSlots) * kSlotBytes + warp * kWarpRawBytes) + tc * (8 * K);
+      const uint32_t* own = tile + q * K;
+      if constexpr (K % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < K / 4; ++i) {
+          const uint4 t = *reinterpret_cast<const uint4*>(own + 4 * i);
+          V[4 * i + 1] = t.x; V[4 * i + 2] = t.y; V[4 * i + 3] = t.z; V[4 * i + 4] = t.w;
+        }
+      } else if constexpr (K % 2 == 0) {
+#pragma unroll
+        for (int i = 0; i < K / 2; ++i) {
+          const uint2 t = *reinterpret_cast<const uint2*>(own + 2 * i);
+          V[2 * i + 1] = t.x; V[2 * i + 2] = t.y;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < K; ++k) V[k + 1] = own[k];
+      }
+      V[0] = tile[history_word<K>(q)];
+    }
+    unsigned char* a_tile = stage0 + s * kATileBytes;
 
     // ---- A: 32 codebook integers of this lane unit as fp16 (1024 + bytesum), rows 2q and 2q+1 of strip `warp`
     {
@@ -220,22 +268,12 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
         }
       }
     }
-    // ---- B: the hi and lo planes of the activations for these 64 columns, [2*np rows][64] in the canonical layout
-    {
-      const int k0 = tile_col0 * 16;
-      for (int v = tid; v < ncols * 8; v += kGemmThreads) {
-        const int row = v % ncols, kc = v / ncols;           // row fastest: conflict-free 16-byte stores
-        const __half* src = (row < np ? p.xh + (size_t)row * n : p.xl + (size_t)(row - np) * n) + k0 + kc * 8;
-        const uint4 val = __ldg(reinterpret_cast<const uint4*>(src));
-        *reinterpret_cast<uint4*>(b_tile + (row >> 3) * kSbo + (row & 7) * 16 + kc * kLbo) = val;
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the tensor core
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (tid == 0 && !failed && !s_fail) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_addr = stage0_addr + s * stage_bytes, b_addr = a_addr + kATileBytes;
+      const uint32_t a_addr = stage0_addr + s * kATileBytes, b_addr = b_stage0_addr + (ch % kBStages) * b_tile_bytes;
 #pragma unroll
       for (int kk = 0; kk < kChunkK / 16; ++kk)
         umma_f16(tmem_base, umma_desc(a_addr + kk * 2 * kLbo, kSbo), umma_desc(b_addr + kk * 2 * kLbo, kSbo), idesc, (ch | kk) ? 1u : 0u);
@@ -243,6 +281,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
     }
     if (failed) s_fail = 1;
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 
   // ---- all MMAs of this CTA done?  (the last commit covers every earlier MMA)
   if (chunks > 0 && !failed) {
@@ -263,9 +302,13 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
     for (int j0 = (warp >> 2) * 16; j0 < np; j0 += 32) {     // warps 0-3 and 4-7 take alternate groups of 16 batch rows
       float hi[16], lo[16];
       tmem_load16(lane_addr + j0, hi);
-      tmem_load16(lane_addr + np + j0, lo);
+      if (p.planes == 2) {
+        tmem_load16(lane_addr + np + j0, lo);
 #pragma unroll
-      for (int j = 0; j < 16; ++j) result[(j0 + j) * 128 + row] = hi[j] + lo[j];
+        for (int j = 0; j < 16; ++j) hi[j] += lo[j];
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) result[(j0 + j) * 128 + row] = hi[j];
     }
   } else {
     for (int e = tid; e < np * 128; e += kGemmThreads) result[e] = 0.f;
@@ -319,8 +362,8 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
   }
 }
 
-int run_rht_f16(const void* x, int dtype, int rows, int np, int n, const uint8_t* su, __half* xh, __half* xl, float* xsum, float* tok,
-                cudaStream_t st);
+int run_rht_f16(const void* x, int dtype, int rows, int np, int n, int planes, const uint8_t* su, __half* xh, __half* xl, float* xsum,
+                float* tok, cudaStream_t st);
 template <int K>
 int launch_packed_gemm_tc(const GemmParams& p, int grid, cudaStream_t st);
 

@@ -7,8 +7,10 @@ for one B200 (148 SMs, HBM3e) rather than copied from the 40-CU part the referen
   M == 0            empty result                                             (htr/ops.py:73-74)
   1 <= M <= 8       one launch of the streaming GEMV (activation transform, decode + dot, split reduce,
                     output transform fused)                                  (replaces htr/ops.py:75-76,95-101)
-  M > 8             the tensor-core packed GEMM (tcgen05 + TMEM), 128 activation rows per launch; decoded tiles go
-                    straight into the MMA operand                            (replaces htr/ops.py:77-93)
+  8 < M <= 128      the tensor-core packed GEMM (tcgen05 + TMEM); decoded tiles go straight into the MMA operand
+                                                                             (replaces htr/ops.py:77-93)
+  M > 128           original-basis bf16 weight from the dequant kernel (decoded once), then a library GEMM
+                                                                             (htr/ops.py:89-93)
   HTR_GEMM=0        instead: GEMV over 8-row chunks up to HTR_GEMV_LOOP_MAX rows, beyond that the original-basis bf16
                     weight from the dequant kernel + a library GEMM (the reference's own routes, kept for comparison)
 
@@ -26,6 +28,8 @@ GEMV_MAX_M = _lib.GEMV_MAX_ROWS
 GEMV_LOOP_MAX = int(os.environ.get("HTR_GEMV_LOOP_MAX", "64"))
 USE_GEMM = os.environ.get("HTR_GEMM", "1") == "1"
 GEMM_MAX_M = _lib.GEMM_MAX_ROWS
+# above this many rows the weight is decoded once to bf16 and a library GEMM runs (the packed GEMM decodes per 128-row chunk)
+GEMM_ROUTE_MAX = int(os.environ.get("HTR_GEMM_ROUTE_MAX", "128"))
 
 _FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
 
@@ -143,13 +147,14 @@ def _linear_impl(x2, qweight, scales, su, sv, bias):
     qweight, scales, su, sv = qweight.contiguous(), scales.contiguous(), su.contiguous(), sv.contiguous()
     bias = None if bias is None else bias.contiguous()
     with torch.cuda.device(x2.device):
-        if M > GEMV_MAX_M and USE_GEMM:
+        if GEMV_MAX_M < M <= GEMM_ROUTE_MAX and USE_GEMM:
             y = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
-            for r0 in range(0, M, GEMM_MAX_M):
-                r1 = min(M, r0 + GEMM_MAX_M)
+            step = _lib.GEMM_MAX_ROWS_F32 if x2.dtype == torch.float32 else GEMM_MAX_M
+            for r0 in range(0, M, step):
+                r1 = min(M, r0 + step)
                 _gemm(x2[r0:r1], qweight, scales, su, sv, bias, y[r0:r1])
             return y
-        if M <= GEMV_LOOP_MAX:
+        if M <= GEMV_LOOP_MAX and not (USE_GEMM and M > GEMV_MAX_M):
             y = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
             for r0 in range(0, M, GEMV_MAX_M):
                 r1 = min(M, r0 + GEMV_MAX_M)

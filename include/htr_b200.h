@@ -101,8 +101,10 @@ int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int 
  * htr_linear_gemm_error_offset(): non-zero after a call means a bounded device-side wait expired and the output is
  * invalid.  Stands in for the prefill branch of _linear_impl, dequant_w + F.linear (htr/ops.py:89-93). */
 #define HTR_GEMM_MAX_ROWS 128
+#define HTR_GEMM_MAX_ROWS_F32 64 /* float32 activations travel as two fp16 planes: half as many rows per call */
 size_t htr_linear_gemm_workspace_bytes(int M, int m, int n, int K);
 size_t htr_linear_gemm_error_offset(void);
+int htr_linear_gemm_last_cuda_error(void);
 int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
                     const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
                     size_t workspace_bytes, htr_stream_t stream);
