@@ -138,7 +138,9 @@ def base_line(args, impl=None):
          "config": {"workload": "mlp_bitrate_sweep_batch1", "shapes_m_x_n": [list(s) for s in SHAPES], "K": list(WIDTHS), "batch": 1,
                     "copies_per_shape_and_K": COPIES, "activations": "bf16 N(0,1)",
                     "l2_policy": "inputs larger than L2: every K-group of a pass holds >= 201 MB of distinct packed weights",
-                    "sharding": "rows" if args.gpus > 1 else "none"}}
+                    "sharding": "rows" if args.gpus > 1 else "none",
+                    "gather": (os.environ.get("HTR_BENCH_GATHER", "peer") + " (epilogue stores into every rank's buffer over NVLink + one barrier per K-group)"
+                               if os.environ.get("HTR_BENCH_GATHER", "peer") == "peer" else "nccl all-gather on a side stream") if args.gpus > 1 else "none"}}
     if impl:
         d["impl"] = impl
     return d
@@ -198,16 +200,37 @@ def run_ours(args):
                 total_bytes += payload_bytes(m, n, K)
                 launches += 1
         groups.append(items)
-    side = torch.cuda.Stream(device=dev)         # the all-gather of one linear overlaps the next linear
+    # N > 1: every rank's epilogue stores its rows into all ranks' gather buffers (symmetric memory, plain NVLink stores);
+    # one cross-rank barrier per K-group orders the ranks.  HTR_BENCH_GATHER=nccl uses NCCL all-gathers on a side stream instead.
+    side = torch.cuda.Stream(device=dev)
+    gather_mode = os.environ.get("HTR_BENCH_GATHER", "peer") if world > 1 else "none"
+    hdl = None
+    if gather_mode == "peer":
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        elems = sum(world * it["m"] for items in groups for it in items)
+        pool = symm_mem.empty(elems, dtype=torch.bfloat16, device=dev)
+        hdl = symm_mem.rendezvous(pool, dist.group.WORLD)
+        bases = [int(p) for p in hdl.buffer_ptrs]
+        off = 0
+        for items in groups:
+            for it in items:
+                it["gathered"] = pool[off:off + world * it["m"]].view(world, it["m"])
+                it["peers"] = [b + off * 2 for b in bases]
+                off += world * it["m"]
 
     def run_group(items, from_host=False):
         main = torch.cuda.current_stream()
         for it in items:
             if from_host:
                 it["xd"].copy_(it["xh"], non_blocking=True)
-            y = ops.linear(it["xd"] if from_host else it["x"], *it["w"])
-            out = y
-            if it["gathered"] is not None:
+            xin = it["xd"] if from_host else it["x"]
+            if gather_mode == "peer":
+                ops.linear_into_peers(xin, *it["w"], None, it["peers"], rank * it["m"])
+                continue
+            y = ops.linear(xin, *it["w"])
+            if gather_mode == "nccl":
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
                     dist.all_gather_into_tensor(it["gathered"], y)
@@ -215,9 +238,14 @@ def run_ours(args):
                         it["yh"].copy_(it["gathered"], non_blocking=True)
                 y.record_stream(side)
             elif from_host:
-                it["yh"].copy_(out, non_blocking=True)
-        if world > 1:
+                it["yh"].copy_(y, non_blocking=True)
+        if gather_mode == "nccl":
             main.wait_stream(side)
+        if gather_mode == "peer":
+            hdl.barrier(channel=0)
+            if from_host:
+                for it in items:
+                    it["yh"].copy_(it["gathered"], non_blocking=True)
 
     # warm every kernel, the workspace and NCCL, then capture CUDA graphs (one per K-group and launch form)
     for items in groups:
@@ -226,17 +254,24 @@ def run_ours(args):
     torch.cuda.synchronize()
     use_graphs = not args.no_graphs
 
+    graph_note = []
+
     def capture(independent=False, from_host=False):
         out = []
-        for items in groups:
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                if independent:
-                    with ops.independent_inputs():
+        try:
+            for items in groups:
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    if independent:
+                        with ops.independent_inputs():
+                            run_group(items, from_host)
+                    else:
                         run_group(items, from_host)
-                else:
-                    run_group(items, from_host)
-            out.append(gr)
+                out.append(gr)
+        except Exception as e:                   # e.g. a collective that cannot be captured: time eager launches instead
+            graph_note.append(f"capture failed ({type(e).__name__}); eager launches")
+            torch.cuda.synchronize()
+            return None
         return out
 
     def barrier():
@@ -319,7 +354,7 @@ def run_ours(args):
                               "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / launches,
                               "per_K": per_k},
                     overlapped=overlapped,
-                    timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs else "eager launches"))
+                    timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs and not graph_note else "eager launches " + "; ".join(graph_note)))
         line["roofline"]["traffic"] = round(1.0215 * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, sample = cpu_sample()

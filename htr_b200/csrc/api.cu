@@ -194,12 +194,21 @@ int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int
 int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
                   const uint8_t* sv, const void* bias, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream,
                   unsigned flags) {
+  return htr_linear_peers(x, dtype, M, qweight, mt, nt, K, scales, su, sv, bias, y, nullptr, 0, 0, workspace, workspace_bytes, stream, flags);
+}
+
+int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                     const uint8_t* sv, const void* bias, void* y, void* const* peer_y, int npeer, int64_t peer_offset, void* workspace,
+                     size_t workspace_bytes, htr_stream_t stream, unsigned flags) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (M < 0 || M > HTR_GEMV_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
   if (mt / 8 > kCounterBytes / 4 || (long long)(mt / 8) * (nt / 4) > 0x3FFFFFFFll) return HTR_ERR_TOO_LARGE;
   if (M == 0) return HTR_OK;
-  if (!x || !qweight || !scales || !su || !sv || !y) return HTR_ERR_NULL;
+  if (npeer < 0 || npeer > 8 || (npeer > 0 && !peer_y) || peer_offset < 0 || (peer_offset & 7)) return HTR_ERR_BAD_SHAPE;
+  if (!x || !qweight || !scales || !su || !sv || (!y && npeer == 0)) return HTR_ERR_NULL;
+  for (int i = 0; i < npeer; ++i)
+    if (!peer_y[i] || !aligned16(peer_y[i])) return HTR_ERR_ALIGNMENT;
   if (!aligned16(x) || !aligned16(qweight) || !aligned16(y) || (bias && !aligned16(bias)) || !aligned16(workspace) ||
       !aligned16(scales))
     return HTR_ERR_ALIGNMENT;
@@ -228,6 +237,9 @@ int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, 
   p.units = pl.units;
   p.split = pl.split;
   p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
+  p.npeer = npeer;
+  p.peer_offset = peer_offset;
+  for (int i = 0; i < 8; ++i) p.peer_y[i] = i < npeer ? peer_y[i] : nullptr;
   p.slots = pl.slots;
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -74,7 +74,12 @@ struct GemvParams {
   int split;        // > 0: every row block is shared by exactly `split` CTAs (grid = row blocks * split); 0: flat unit ranges
   int slots;        // partial slots per row block
   int independent;  // 1: x, bias and y are untouched by the preceding kernel of the stream (wait only before publishing)
-  float cb;         // 1 / rms of the codebook integers
+  float cb;
+  // Peer form (row-sharded linears over NVLink): when npeer > 0 the epilogue writes its rows into every listed buffer
+  // (peers' and its own, plain stores through peer-mapped addresses) at element offset peer_offset, instead of into y.
+  void* peer_y[8];
+  int npeer;
+  long long peer_offset;         // 1 / rms of the codebook integers
 };
 
 // owner CTA of unit x when CTA b starts at floor(b*U/G)
@@ -384,7 +389,12 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
                              flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
       o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
-      store_quad(p.y, (size_t)r * m + row0, p.dtype, o);
+      if (p.npeer == 0) {
+        store_quad(p.y, (size_t)r * m + row0, p.dtype, o);
+      } else {
+#pragma unroll 1
+        for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);
+      }
     }
     if (cgi == CG) { cgi = 0; ++rb; }
     HTR_TRACE(5);

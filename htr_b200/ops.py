@@ -121,6 +121,28 @@ def gemm_error_codes():
     return [int(ws[off:off + 4].view(torch.int32).item()) for ws in _GEMM_WS.values()]
 
 
+def linear_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset):
+    """Row-shard form of the GEMV (M <= 8): the result rows [M, m_local] are stored, from inside the kernel, at element
+    offset `elem_offset` of every buffer in `peer_ptrs` (device addresses of the gather buffers of all ranks as mapped
+    into this process).  Nothing is returned; the caller orders the ranks (a barrier) before reading the buffers."""
+    _check(x2, qweight, scales, su, sv, bias)
+    M = x2.shape[0]
+    if not 1 <= M <= GEMV_MAX_M:
+        raise _lib.HTRError("linear_into_peers handles 1..8 activation rows")
+    mt, nt, W = qweight.shape
+    K = W // 8
+    need = _lib.lib.htr_linear_workspace_bytes(M, mt * 16, nt * 16, K)
+    ws = workspace(x2.device, need)
+    st = torch.cuda.current_stream(x2.device).cuda_stream
+    import ctypes
+
+    arr = (ctypes.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
+    rc = _lib.lib.htr_linear_peers(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
+                                   sv.data_ptr(), None if bias is None else bias.data_ptr(), None, arr, len(peer_ptrs), int(elem_offset),
+                                   ws.data_ptr(), ws.numel(), st, _FLAGS)
+    _lib.check(rc, "htr_linear_peers")
+
+
 class independent_inputs:
     """Context manager: inside it, every packed linear promises that its activations, bias and output are not
     touched by the kernel launched just before it on the stream (e.g. the experts of one MoE layer, or the

@@ -83,10 +83,47 @@ def all_gather_rows(y_local, group=None):
     return torch.stack(parts)
 
 
-class RowShardedLinear:
-    """y = x @ W^T (+bias) with W's rows dealt to the ranks of `group`; every rank gets the full [.., m] result."""
+class PeerGather:
+    """Gather buffers in symmetric memory: every rank maps every rank's buffer, so a kernel can store its output rows
+    straight into all of them over NVLink (htr_linear_peers) and no collective kernel runs.  `barrier()` orders the
+    ranks on the current stream: after it, every rank's rows are in this rank's buffer.
 
-    def __init__(self, qweight, scales, su, sv, bias=None, group=None, device=None, linear_fn=None):
+    Two alternating buffers let a fast rank start the next call while a slow one still reads the previous result."""
+
+    def __init__(self, world, rank, max_rows, rows_per_rank, dtype, device, group=None):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer stores only, no NVLink multicast objects
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.world, self.rank, self.max_rows, self.rows_per_rank = world, rank, max_rows, rows_per_rank
+        self.buf = symm_mem.empty((2, world, max_rows, rows_per_rank), dtype=dtype, device=device)
+        self.hdl = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.flip = 0
+        self.esize = self.buf.element_size()
+
+    def target(self):
+        """(peer addresses of the buffer half in use, element offset of this rank's block inside it)"""
+        half = self.flip * self.world * self.max_rows * self.rows_per_rank
+        return [p + half * self.esize for p in self.ptrs], self.rank * self.max_rows * self.rows_per_rank
+
+    def barrier(self):
+        self.hdl.barrier(channel=0)
+
+    def result(self, rows):
+        out = self.buf[self.flip, :, :rows, :]
+        self.flip ^= 1
+        return out
+
+
+class RowShardedLinear:
+    """y = x @ W^T (+bias) with W's rows dealt to the ranks of `group`; every rank gets the full [.., m] result.
+
+    gather="nccl": all-gather of the local outputs.  gather="peer": the GEMV's epilogue stores its rows into every rank's
+    gather buffer itself (up to 8 activation rows; larger batches fall back to the all-gather)."""
+
+    def __init__(self, qweight, scales, su, sv, bias=None, group=None, device=None, linear_fn=None, gather="nccl", dtype=torch.bfloat16):
         self.group = group
         self.world, self.rank = _world(group)
         self.m = qweight.shape[0] * 16
@@ -97,6 +134,9 @@ class RowShardedLinear:
         self.su = su.to(dev).contiguous()
         self.bias = None if b is None else b.to(dev)
         self.linear_fn = linear_fn or _default_linear()
+        self.peer = None
+        if gather == "peer" and self.world > 1:
+            self.peer = PeerGather(self.world, self.rank, 8, self.qweight.shape[0] * 16, dtype, dev, group)
 
     def local(self, x):
         """This rank's slice of the output, [.., rows_per_rank] (padding rows are zero)."""
@@ -105,9 +145,21 @@ class RowShardedLinear:
 
     def __call__(self, x):
         lead = x.shape[:-1]
-        y = self.local(x.reshape(-1, self.n))
-        g = all_gather_rows(y, self.group)                                   # [world, M, rows_per_rank]
-        full = g.permute(1, 0, 2).reshape(y.shape[0], -1)[:, :self.m]
+        x2 = x.reshape(-1, self.n)
+        if self.peer is not None and 1 <= x2.shape[0] <= 8 and x2.dtype == self.peer.buf.dtype:
+            from . import ops
+
+            ptrs, off = self.peer.target()
+            bias = None if self.bias is None else self.bias.to(x2.dtype)
+            ops.linear_into_peers(x2.contiguous(), self.qweight, self.scales, self.su, self.sv, bias, ptrs, off)
+            self.peer.barrier()
+            g = self.peer.result(x2.shape[0])                                # [world, M, rows_per_rank]
+            rows = x2.shape[0]
+        else:
+            y = self.local(x2)
+            g = all_gather_rows(y, self.group)                               # [world, M, rows_per_rank]
+            rows = y.shape[0]
+        full = g.permute(1, 0, 2).reshape(rows, -1)[:, :self.m]
         return full.reshape(*lead, self.m)
 
 

@@ -82,6 +82,17 @@ int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, 
                   const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
                   size_t workspace_bytes, htr_stream_t stream, unsigned flags);
 
+/* htr_linear_ex for a row shard of a taller linear on one NVLink box: with npeer > 0 the epilogue stores the result rows
+ * into every buffer of peer_y[0..npeer) (device addresses of this and the peer GPUs' gather buffers as mapped into this
+ * process, e.g. by CUDA IPC or torch symmetric memory) at element offset peer_offset, with plain stores, and y is not
+ * written.  The stores are complete when the kernel is; consumers on other GPUs still need their own ordering (a
+ * barrier across the ranks) before they read.  peer_offset must be a multiple of 8 elements.  (No counterpart in the
+ * reference, which is single-GPU: htr/vllm_plugin.py:91.) */
+int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+                     const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y /* may be NULL when npeer > 0 */,
+                     void* const* peer_y, int npeer, int64_t peer_offset, void* workspace, size_t workspace_bytes,
+                     htr_stream_t stream, unsigned flags);
+
 /* htr_linear without a workspace argument, for callers that cannot allocate device memory when they need the
  * linear (stream capture in progress, allocation-free real-time loops, hosts whose allocator is not theirs to call).
  * The scratch is a fixed array of HTR_STATIC_WORKSPACE_BYTES inside the library image, held by every GPU that

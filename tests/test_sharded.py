@@ -155,7 +155,15 @@ def _nccl_worker(rank, world, port, q):
         x = torch.randn(3, 1024, generator=torch.Generator().manual_seed(9)).bfloat16().to(dev)
         y = RowShardedLinear(qw, sc, su, sv, device=dev)(x)
         full = ops.linear(x, qw.to(dev), sc.to(dev), su.to(dev), sv.to(dev))
-        q.put((rank, bool(torch.equal(y, full)), tuple(y.shape)))
+        ok = bool(torch.equal(y, full))
+        # the same through peer stores from the kernel epilogue (symmetric memory, no collective kernel), three calls in a row
+        peer = RowShardedLinear(qw, sc, su, sv, device=dev, gather="peer")
+        for i in range(3):
+            xi = (x * (i + 1)).contiguous()
+            want = ops.linear(xi, qw.to(dev), sc.to(dev), su.to(dev), sv.to(dev))
+            ok = ok and bool(torch.equal(peer(xi), want))
+        torch.cuda.synchronize()
+        q.put((rank, ok, tuple(y.shape)))
     finally:
         dist.destroy_process_group()
 
