@@ -12,7 +12,9 @@ distinct copies so that every K-group alone is larger than the 126 MB L2: one st
 them, so no launch finds its weights in cache.
 
 One JSON line is printed by rank 0:
-  value     device-resident throughput of the whole pass, CUDA-event timed, max over ranks
+  value     device-resident throughput of the whole pass, CUDA-event timed, max over ranks; the linears of a pass are
+            independent, so they are launched with HTR_LINEAR_INPUT_INDEPENDENT (consecutive launches overlap);
+            `stream_ordered` repeats the pass in the default form, in which each launch waits for its predecessor
   e2e       the same pass through the public operator (htr_b200.ops.linear) with the activations in pinned
             host memory and the outputs copied back to pinned host memory inside the timed region
   roofline  of the GEMV kernel: achieved = algorithmic packed bytes per launch / average launch duration,
@@ -137,6 +139,8 @@ def base_line(args, impl=None):
          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
          "config": {"workload": "mlp_bitrate_sweep_batch1", "shapes_m_x_n": [list(s) for s in SHAPES], "K": list(WIDTHS), "batch": 1,
                     "copies_per_shape_and_K": COPIES, "activations": "bf16 N(0,1)",
+                    "launch_form": "independent linears: htr_linear_ex(HTR_LINEAR_INPUT_INDEPENDENT), consecutive launches overlap; "
+                                   "stream_ordered gives the default form",
                     "l2_policy": "inputs larger than L2: every K-group of a pass holds >= 201 MB of distinct packed weights",
                     "sharding": "rows" if args.gpus > 1 else "none",
                     "gather": (os.environ.get("HTR_BENCH_GATHER", "peer") + " (epilogue stores into every rank's buffer over NVLink + one barrier per K-group)"
@@ -310,9 +314,11 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms, per_k_ms = timed(capture() if use_graphs else None, args.steps)
-    # the same pass with every launch declared independent of its predecessor (htr_linear_ex flag): launches overlap
-    ov_ms, ov_per_k_ms = timed(capture(independent=True) if use_graphs else None, args.steps, independent=True)
+    # The linears of a pass do not feed one another, so they are launched the way the library asks for such work:
+    # declared independent of their predecessor (HTR_LINEAR_INPUT_INDEPENDENT), which lets consecutive launches overlap.
+    ms, per_k_ms = timed(capture(independent=True) if use_graphs else None, args.steps, independent=True)
+    # the same pass in the default, stream-ordered form (what a chain of dependent linears gets)
+    ov_ms, ov_per_k_ms = timed(capture() if use_graphs else None, args.steps)
     # end to end through the public operator: activations from pinned host memory, outputs back to pinned host memory
     e2e_steps = max(1, min(args.steps, 10))
     e2e_ms, _ = timed(capture(from_host=True) if use_graphs else None, e2e_steps, from_host=True)
@@ -339,7 +345,7 @@ def run_ours(args):
             per_k[f"K{K}"] = {"GBps_per_gpu": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                               "us_per_launch": round(1e3 * per_k_ms[i] / (len(SHAPES) * COPIES), 3)}
         ogbs = total_bytes * args.steps / (ov_ms * 1e-3) / 1e9
-        overlapped = {"what": "same pass, launches flagged HTR_LINEAR_INPUT_INDEPENDENT (each overlaps its predecessor)",
+        overlapped = {"what": "same pass, default launch form: every launch waits for its predecessor before reading activations",
                       "value": ogbs * world, "unit": "GB/s", "frac_of_peak_per_gpu": ogbs / peak,
                       "per_K": {f"K{K}": round(sum(payload_bytes(m, n, K) for (m, n) in SHAPES) * COPIES / (ov_per_k_ms[i] * 1e-3) / 1e9, 1)
                                 for i, K in enumerate(WIDTHS)}}
@@ -353,13 +359,118 @@ def run_ours(args):
                                               "algorithmic (profiles/); 1.02x, proportional to packed bytes",
                               "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / launches,
                               "per_K": per_k},
-                    overlapped=overlapped,
+                    stream_ordered=overlapped,
                     timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs and not graph_note else "eager launches " + "; ".join(graph_note)))
         line["roofline"]["traffic"] = round(1.0215 * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, sample = cpu_sample()
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
         print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_extra(args):
+    """Further workloads of the benchmark configurations, one GPU (or N ranks for the sharded LM head):
+    lmhead   151936x4096 K4 LM head, batch 1 and 8, rows sharded over the ranks (strong scaling), peer-store gather
+    decoder  the 9B-class dense decoder, K4 trunk + K4 head, 16-token prompt + 256 greedy tokens, one sequence
+    moe      64 experts, top-8, SwiGLU 4096->1536->4096, K3, 1..32 tokens per step
+    Prints one JSON line per workload (rank 0)."""
+    import torch
+    import torch.distributed as dist
+    from htr_b200 import ops, wire
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peak, peak_kind = measured_peak()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def time_graph(fn, reps):
+        fn(); sync_all()
+        g = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(g):
+                fn()
+            run = g.replay
+        except Exception:
+            torch.cuda.synchronize()
+            run = fn
+        for _ in range(3):
+            run()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        sync_all()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    if args.workload == "lmhead":
+        from htr_b200.sharded import RowShardedLinear
+        m, n, K = 151936, 4096, 4
+        copies = 3                                              # distinct heads rotate so that no launch finds its shard in L2
+        heads = []
+        for c in range(copies):
+            qw, sc, su, sv = wire.random_packed(m, n, K, seed=300 + c)
+            heads.append(RowShardedLinear(qw, sc, su, sv, device=dev, gather="peer" if world > 1 else "nccl"))
+        for M in (1, 8):
+            x = torch.randn(M, n, device=dev).bfloat16()
+            ms = time_graph(lambda: [h(x) for h in heads], args.steps) / copies
+            if rank == 0:
+                gbs = payload_bytes(m, n, K) / (ms * 1e-3) / 1e9
+                print(json.dumps({"metric": "lm_head_packed_GBps", "unit": "GB/s", "value": gbs, "n_gpus": world, "scaling": "strong",
+                                  "ms_per_step": ms, "frac_of_peak_per_gpu": gbs / world / peak, "tokens_per_s": M / (ms * 1e-3),
+                                  "config": {"workload": "lm_head_151936x4096_K4_row_sharded", "batch": M, "gather": "peer stores + barrier" if world > 1 else "none"}}), flush=True)
+    elif args.workload == "decoder":
+        from htr_b200.decoder import DecoderConfig, PackedDecoder
+        model = PackedDecoder(DecoderConfig(), dev, seed=1)
+        prompt = torch.randint(0, 151936, (16,), generator=torch.Generator().manual_seed(2))
+        model.generate(prompt, 8)                               # warm-up
+        toks, t_prompt, t_decode = model.generate(prompt, 256)
+        bpt = model.packed_bytes_per_token()
+        print(json.dumps({"metric": "decode_tokens_per_s", "unit": "tok/s", "value": 256 / t_decode, "n_gpus": 1,
+                          "wall_tokens_per_s_incl_prompt": 256 / (t_prompt + t_decode), "prompt_s": t_prompt, "decode_s": t_decode,
+                          "packed_GBps": bpt * 256 / t_decode / 1e9, "frac_of_peak": bpt * 256 / t_decode / 1e9 / peak,
+                          "packed_bytes_per_token": bpt,
+                          "config": {"workload": "dense_9b_class_K4_trunk_K4_head", "prompt": 16, "new_tokens": 256, "batch": 1,
+                                     "weights": "random packed", "graph": "one CUDA graph per decode step"}}), flush=True)
+    elif args.workload == "moe":
+        from htr_b200.sharded import ExpertParallelMoE
+        E, h, inter, K = 64, 4096, 1536, 3
+        experts = [dict(gate_up=wire.random_packed(2 * inter, h, K, seed=2 * e), down=wire.random_packed(h, inter, K, seed=2 * e + 1)) for e in range(E)]
+        moe = ExpertParallelMoE(experts, device=dev)
+        g = torch.Generator().manual_seed(0)
+        for T in (1, 4, 8, 32):
+            x = torch.randn(T, h, generator=g).bfloat16().to(dev)
+            ids = torch.stack([torch.randperm(E, generator=g)[:8] for _ in range(T)])
+            w = torch.rand(T, 8, generator=g); w = (w / w.sum(-1, keepdim=True)).to(dev)
+            moe(x, ids, w); sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                moe(x, ids, w)
+            e1.record(); sync_all()
+            ms = e0.elapsed_time(e1) / args.steps
+            active = len(set(ids.flatten().tolist()))
+            nbytes = active * (payload_bytes(2 * inter, h, K) + payload_bytes(h, inter, K)) / max(world, 1)
+            if rank == 0:
+                print(json.dumps({"metric": "moe_layer_ms", "unit": "ms", "value": ms, "higher_is_better": False, "n_gpus": world,
+                                  "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "packed_GBps_per_gpu": nbytes / (ms * 1e-3) / 1e9,
+                                  "config": {"workload": "moe_64x_top8_swiglu_4096_1536_K3", "tokens": T, "routing": "host-resolved, per-expert launches"}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -372,9 +483,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--workload", default="mlp", choices=("mlp", "lmhead", "decoder", "moe"),
+                    help="mlp = the default benchmark line; the others print lines for the remaining configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "mlp":
+        run_extra(args)
     else:
         run_ours(args)
 

@@ -1,0 +1,147 @@
+"""Minimal dense decoder whose linears are HTR-W1 packed: the caller that turns packed-GEMV GB/s into decode tokens/s.
+
+Stands in for the model code that surrounds `HTRLinearMethod.apply` in a serving stack (htr/vllm_plugin.py:130-138) for
+the reference's headline case: a 9B-class dense decoder (36 layers, hidden 4096, 32 query / 8 KV heads of 128, SwiGLU
+12288, vocabulary 151936), every trunk linear and the LM head packed, norms and embeddings bf16, one sequence, greedy
+decoding (docs/case-studies/dense-9b.md of the reference).  Weights are random (no checkpoint is available); fused
+projections (q|k|v, gate|up) are single packed linears, as the format prescribes (docs/FORMAT.md:31-32).
+
+Every packed linear goes through `htr_b200.ops.linear`; the rest (RMSNorm, rotary embedding, attention over a static
+KV cache, SwiGLU) are plain torch ops.  A decode step reads its position from a device tensor, so one CUDA graph
+captured once serves every step.
+"""
+import dataclasses
+import math
+
+import torch
+
+from . import ops, wire
+
+
+@dataclasses.dataclass
+class DecoderConfig:
+    layers: int = 36
+    hidden: int = 4096
+    q_heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    intermediate: int = 12288
+    vocab: int = 151936
+    K: int = 4                 # bits per weight of the trunk
+    K_head: int = 4            # bits per weight of the LM head
+    max_len: int = 512
+    rope_theta: float = 1.0e6
+    eps: float = 1.0e-6
+
+
+def _rms_norm(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class PackedDecoder:
+    def __init__(self, cfg, device, seed=0, dtype=torch.bfloat16):
+        self.cfg, self.device, self.dtype = cfg, device, dtype
+        g = torch.Generator().manual_seed(seed)
+        c = cfg
+        qkv_out = (c.q_heads + 2 * c.kv_heads) * c.head_dim
+
+        def packed(m, n, K, s):
+            return wire.random_packed(m, n, K, seed=seed * 100003 + s, device=device)
+
+        self.layers = []
+        for i in range(c.layers):
+            self.layers.append(dict(
+                qkv=packed(qkv_out, c.hidden, c.K, 10 * i + 1), o=packed(c.hidden, c.q_heads * c.head_dim, c.K, 10 * i + 2),
+                gate_up=packed(2 * c.intermediate, c.hidden, c.K, 10 * i + 3), down=packed(c.hidden, c.intermediate, c.K, 10 * i + 4),
+                ln1=torch.ones(c.hidden, dtype=dtype, device=device), ln2=torch.ones(c.hidden, dtype=dtype, device=device)))
+        self.head = packed(c.vocab, c.hidden, c.K_head, 7)
+        self.ln_f = torch.ones(c.hidden, dtype=dtype, device=device)
+        self.embed = (torch.randn(c.vocab, c.hidden, generator=g) * 0.02).to(dtype).to(device)
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2).float() / c.head_dim))
+        ang = torch.arange(c.max_len).float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos().to(device), ang.sin().to(device)
+        self.k_cache = torch.zeros(c.layers, c.max_len, c.kv_heads, c.head_dim, dtype=dtype, device=device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.arange = torch.arange(c.max_len, device=device)
+
+    def packed_bytes_per_token(self):
+        """Packed payload read by one decode step (every trunk linear once + the LM head)."""
+        c = self.cfg
+        qkv_out = (c.q_heads + 2 * c.kv_heads) * c.head_dim
+        per_layer = (wire.payload_bytes(qkv_out, c.hidden, c.K) + wire.payload_bytes(c.hidden, c.q_heads * c.head_dim, c.K) +
+                     wire.payload_bytes(2 * c.intermediate, c.hidden, c.K) + wire.payload_bytes(c.hidden, c.intermediate, c.K))
+        return c.layers * per_layer + wire.payload_bytes(c.vocab, c.hidden, c.K_head)
+
+    def _rope(self, t, pos):
+        cos, sin = self.cos.index_select(0, pos)[:, None, :], self.sin.index_select(0, pos)[:, None, :]
+        t1, t2 = t[..., ::2].float(), t[..., 1::2].float()
+        out = torch.stack((t1 * cos - t2 * sin, t1 * sin + t2 * cos), dim=-1)
+        return out.flatten(-2).to(t.dtype)
+
+    def forward(self, ids, pos):
+        """ids [T] token ids, pos [T] their positions (device tensors).  Returns logits [T, vocab] and updates the cache."""
+        c = self.cfg
+        T = ids.shape[0]
+        x = self.embed.index_select(0, ids)
+        # a query at position p sees cache slots <= p
+        mask = (self.arange[None, :] <= pos[:, None])[None, None]                     # [1, 1, T, max_len]
+        rep = c.q_heads // c.kv_heads
+        for li, L in enumerate(self.layers):
+            h = _rms_norm(x, L["ln1"], c.eps)
+            qkv = ops.linear(h, *L["qkv"])
+            q, k, v = qkv.split((c.q_heads * c.head_dim, c.kv_heads * c.head_dim, c.kv_heads * c.head_dim), dim=-1)
+            q = self._rope(q.view(T, c.q_heads, c.head_dim), pos)
+            k = self._rope(k.view(T, c.kv_heads, c.head_dim), pos)
+            self.k_cache[li].index_copy_(0, pos, k)
+            self.v_cache[li].index_copy_(0, pos, v.view(T, c.kv_heads, c.head_dim))
+            kk = self.k_cache[li].permute(1, 0, 2).repeat_interleave(rep, dim=0)[None]   # [1, q_heads, max_len, d]
+            vv = self.v_cache[li].permute(1, 0, 2).repeat_interleave(rep, dim=0)[None]
+            att = torch.nn.functional.scaled_dot_product_attention(q.permute(1, 0, 2)[None], kk, vv, attn_mask=mask)
+            x = x + ops.linear(att[0].permute(1, 0, 2).reshape(T, c.q_heads * c.head_dim), *L["o"])
+            h = _rms_norm(x, L["ln2"], c.eps)
+            gu = ops.linear(h, *L["gate_up"])
+            act = torch.nn.functional.silu(gu[:, :c.intermediate]) * gu[:, c.intermediate:]
+            x = x + ops.linear(act, *L["down"])
+        return ops.linear(_rms_norm(x, self.ln_f, c.eps), *self.head)
+
+    @torch.no_grad()
+    def generate(self, prompt_ids, new_tokens, use_graph=True):
+        """Greedy decoding: one forward over the prompt (batched rows), then `new_tokens` single-token steps.
+        Returns (token ids [new_tokens], seconds for the prompt, seconds for the decode steps) measured with CUDA events."""
+        dev = self.device
+        P = prompt_ids.numel()
+        assert P + new_tokens <= self.cfg.max_len
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        cur = torch.zeros(1, dtype=torch.long, device=dev)
+        pos = torch.zeros(1, dtype=torch.long, device=dev)
+        out = torch.zeros(new_tokens, dtype=torch.long, device=dev)
+
+        def step():
+            logits = self.forward(cur, pos)
+            cur.copy_(logits.argmax(-1))
+            pos.add_(1)
+
+        graph = None
+        if use_graph:                                    # warm up and capture before the timed region (cache content is rewritten below)
+            cur.zero_(); pos.fill_(P)
+            step()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            torch.cuda.synchronize()
+        ev[0].record()
+        logits = self.forward(prompt_ids.to(dev), torch.arange(P, device=dev))
+        cur.copy_(logits[-1:].argmax(-1))
+        pos.fill_(P)
+        ev[1].record()
+        for t in range(new_tokens):
+            out[t] = cur[0]
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+        ev[2].record()
+        torch.cuda.synchronize()
+        return out, ev[0].elapsed_time(ev[1]) * 1e-3, ev[1].elapsed_time(ev[2]) * 1e-3
