@@ -237,6 +237,9 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
   p.units = pl.units;
   p.split = pl.split;
   p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
+  p.group = 0;
+  p.rb_per_problem = 0;
+  p.g_x = nullptr; p.g_qw = nullptr; p.g_scales = nullptr; p.g_su = nullptr; p.g_sv = nullptr; p.g_y = nullptr;
   p.npeer = npeer;
   p.peer_offset = peer_offset;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = i < npeer ? peer_y[i] : nullptr;
@@ -251,6 +254,79 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
     case 5: e = launch_packed_gemv<5>(p, pl.rows_t, pl.grid, st); break;
     case 6: e = launch_packed_gemv<6>(p, pl.rows_t, pl.grid, st); break;
     case 8: e = launch_packed_gemv<8>(p, pl.rows_t, pl.grid, st); break;
+  }
+  return e ? cuda_fail(e) : HTR_OK;
+}
+
+size_t htr_linear_grouped_workspace_bytes(int count, int m, int n, int K) {
+  if (!width_ok(K) || count < 1 || m <= 0 || n <= 0 || m % 128 || n % 128) return 0;
+  Plan pl;
+  if (make_plan(1, m, n, K, &pl) != HTR_OK) return 0;
+  // at most n/64 CTAs share a row block
+  return counter_bytes(m) + (size_t)count * (m / 128) * (size_t)(n / 64) * 128 * sizeof(float);
+}
+
+int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* qweight_list, int mt, int nt, int K,
+                       const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, void* const* y_list,
+                       int count, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+  if (!width_ok(K)) return HTR_ERR_BAD_K;
+  if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
+  if (count < 0 || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
+  if (count == 0) return HTR_OK;
+  if (!x_list || !qweight_list || !scales_list || !su_list || !sv_list || !y_list) return HTR_ERR_NULL;
+  const int m = mt * 16, n = nt * 16, rbp = m / 128;
+  if ((long long)count * rbp > kCounterBytes / 4) return HTR_ERR_TOO_LARGE;
+  if (!aligned16(workspace)) return HTR_ERR_ALIGNMENT;
+  Plan pl;
+  const int rc = make_plan(1, m, n, K, &pl);
+  if (rc != HTR_OK) return rc;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int sms = device_sms(dev);
+  const int per_sm = g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, 1);
+  const long long cap = (long long)sms * per_sm;
+  const long long rbs = (long long)count * rbp;
+  long long split = cap / rbs;
+  if (split < 1) split = 1;
+  if (split > pl.cg) split = pl.cg;
+  const size_t need = counter_bytes(m) + (size_t)rbs * (size_t)split * 128 * sizeof(float);
+  if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
+
+  GemvParams p;
+  p.x = nullptr; p.qw = nullptr; p.scales = nullptr; p.su = nullptr; p.sv = nullptr; p.bias = nullptr; p.y = nullptr;
+  p.counters = static_cast<int*>(workspace);
+  p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counter_bytes(m));
+  p.rows = 1;
+  p.mt = mt;
+  p.nt = nt;
+  p.dtype = dtype;
+  p.cg = pl.cg;
+  p.units = (int)(rbs * pl.cg);
+  p.split = (int)split;
+  p.slots = (int)split;
+  p.independent = 0;
+  p.cb = (float)codebook_scale();
+  p.npeer = 0;
+  p.peer_offset = 0;
+  for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
+  p.group = count;
+  p.rb_per_problem = rbp;
+  p.g_x = x_list;
+  p.g_qw = reinterpret_cast<const uint32_t* const*>(qweight_list);
+  p.g_scales = reinterpret_cast<const __half* const*>(scales_list);
+  p.g_su = su_list;
+  p.g_sv = sv_list;
+  p.g_y = y_list;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = (int)(rbs * split);
+  int e = 0;
+  switch (K) {
+    case 2: e = launch_packed_gemv<2>(p, 1, grid, st); break;
+    case 3: e = launch_packed_gemv<3>(p, 1, grid, st); break;
+    case 4: e = launch_packed_gemv<4>(p, 1, grid, st); break;
+    case 5: e = launch_packed_gemv<5>(p, 1, grid, st); break;
+    case 6: e = launch_packed_gemv<6>(p, 1, grid, st); break;
+    case 8: e = launch_packed_gemv<8>(p, 1, grid, st); break;
   }
   return e ? cuda_fail(e) : HTR_OK;
 }

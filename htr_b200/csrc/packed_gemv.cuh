@@ -79,7 +79,17 @@ struct GemvParams {
   // (peers' and its own, plain stores through peer-mapped addresses) at element offset peer_offset, instead of into y.
   void* peer_y[8];
   int npeer;
-  long long peer_offset;         // 1 / rms of the codebook integers
+  long long peer_offset;
+  // Grouped form (experts of a mixture-of-experts layer): group > 0 problems of identical shape, one activation row each;
+  // the per-problem tensors come from device arrays of device pointers, row blocks are numbered problem-major.
+  int group;
+  int rb_per_problem;
+  const void* const* g_x;
+  const uint32_t* const* g_qw;
+  const __half* const* g_scales;
+  const uint8_t* const* g_su;
+  const uint8_t* const* g_sv;
+  void* const* g_y;         // 1 / rms of the codebook integers
 };
 
 // owner CTA of unit x when CTA b starts at floor(b*U/G)
@@ -217,9 +227,29 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
 
   int rb = u_begin / CG, cgi = u_begin - rb * CG;
 
+  // tensors of this CTA's problem (grouped form: one row block per CTA, so they never change inside a launch)
+  const void* x_ptr = p.x;
+  const uint32_t* qw_ptr = p.qw;
+  const __half* scales_ptr = p.scales;
+  const uint8_t* su_ptr = p.su;
+  const uint8_t* sv_ptr = p.sv;
+  void* y_ptr = p.y;
+  int rb_base = 0;
+  if (p.group > 0) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");            // the pointer lists may come from the preceding kernel
+    const int prob = rb / p.rb_per_problem;
+    rb_base = prob * p.rb_per_problem;
+    x_ptr = p.g_x[prob];
+    qw_ptr = p.g_qw[prob];
+    scales_ptr = p.g_scales[prob];
+    su_ptr = p.g_su[prob];
+    sv_ptr = p.g_sv[prob];
+    y_ptr = p.g_y[prob];
+  }
+
   // prefetch cursor: runs kRing units ahead of the consumer along the same unit sequence.  Offsets are kept in
   // 16-byte units relative to this lane's first chunk, so the bookkeeping is 32-bit.
-  const char* lane_base = reinterpret_cast<const char*>(p.qw) + ((size_t)(rb * 8 + 4 * h + g) * nt + (size_t)(4 * cgi + c)) * kTileBytes + q * 16;
+  const char* lane_base = reinterpret_cast<const char*>(qw_ptr) + ((size_t)((rb - rb_base) * 8 + 4 * h + g) * nt + (size_t)(4 * cgi + c)) * kTileBytes + q * 16;
   constexpr int kStep16 = 4 * kTileBytes / 16;                    // next column group: four tiles further along the strip
   const int wrap_extra16 = (7 * nt + 4) * (kTileBytes / 16) - kStep16;   // ... or the first column group of the next row block
   int pf_off16 = 0, pf_left = u_end - u_begin, pf_in_rb = CG - cgi;
@@ -266,7 +296,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     const int items = MT * (hb1 - hb0);
     float4 xv_first = make_float4(0.f, 0.f, 0.f, 0.f);
     if (warp < items && warp / (hb1 - hb0) < p.rows)                // the first item's loads go out before the copy burst
-      xv_first = load_quad(p.x, (size_t)(warp / (hb1 - hb0)) * n + (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.dtype);
+      xv_first = load_quad(x_ptr, (size_t)(warp / (hb1 - hb0)) * n + (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.dtype);
     if (!ring_primed) {
 #pragma unroll
       for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
@@ -276,8 +306,8 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       const int r = item / (hb1 - hb0), hb = hb0 + item % (hb1 - hb0);
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (r < p.rows) {
-        const float4 xv = item == warp ? xv_first : load_quad(p.x, (size_t)r * n + hb * 128 + 4 * lane, p.dtype);
-        const unsigned sg = sign_nibble(p.su, hb * 32 + lane);
+        const float4 xv = item == warp ? xv_first : load_quad(x_ptr, (size_t)r * n + hb * 128 + 4 * lane, p.dtype);
+        const unsigned sg = sign_nibble(su_ptr, hb * 32 + lane);
         v[0] = flip(xv.x, sg & 1u); v[1] = flip(xv.y, (sg >> 1) & 1u); v[2] = flip(xv.z, (sg >> 2) & 1u); v[3] = flip(xv.w, sg >> 3);
         wht128(v, lane);
       }
@@ -332,13 +362,13 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     }
     float* ytil = smem + 4 * MT * 128;                  // [MT][128], disjoint from red (MT*kStageCols >= 5*MT*128)
     // operands of the epilogue are fetched now so that their latency hides behind the arrival handshake
-    const int row0 = rb * 128 + 4 * lane;
+    const int row0 = (rb - rb_base) * 128 + 4 * lane;               // row inside this problem's weight
     uint2 sc_raw = make_uint2(0u, 0u);
     float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
     unsigned sv_bits = 0;
     if (warp < p.rows) {
-      sc_raw = __ldg(reinterpret_cast<const uint2*>(p.scales + row0));
-      sv_bits = sign_nibble(p.sv, rb * 32 + lane);
+      sc_raw = __ldg(reinterpret_cast<const uint2*>(scales_ptr + row0));
+      sv_bits = sign_nibble(sv_ptr, (rb - rb_base) * 32 + lane);
       if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
     }
     if (!predecessor_done) {                           // deferred wait of the independent-input form
@@ -390,7 +420,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
                              flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
       o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
       if (p.npeer == 0) {
-        store_quad(p.y, (size_t)r * m + row0, p.dtype, o);
+        store_quad(y_ptr, (size_t)r * m + row0, p.dtype, o);
       } else {
 #pragma unroll 1
         for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);

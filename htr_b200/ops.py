@@ -143,6 +143,22 @@ def linear_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset)
     _lib.check(rc, "htr_linear_peers")
 
 
+def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K, dtype):
+    """`count` packed linears of one shape in one launch, one activation row each (htr_linear_grouped).  Every argument is
+    an int64 CUDA tensor of `count` device addresses (built on the device, e.g. by indexing per-expert address tables with
+    the routing result), so the call needs no host synchronisation and can be captured in a CUDA graph."""
+    count = x_ptrs.numel()
+    dev = x_ptrs.device
+    need = _lib.lib.htr_linear_grouped_workspace_bytes(count, mt * 16, nt * 16, K)
+    if need == 0:
+        raise _lib.HTRError("htr_linear_grouped: unsupported sizes")
+    ws = workspace(dev, need)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    rc = _lib.lib.htr_linear_grouped(x_ptrs.data_ptr(), _DTYPES[dtype], qw_ptrs.data_ptr(), mt, nt, K, sc_ptrs.data_ptr(), su_ptrs.data_ptr(),
+                                     sv_ptrs.data_ptr(), y_ptrs.data_ptr(), count, ws.data_ptr(), ws.numel(), st)
+    _lib.check(rc, "htr_linear_grouped")
+
+
 class independent_inputs:
     """Context manager: inside it, every packed linear promises that its activations, bias and output are not
     touched by the kernel launched just before it on the stream (e.g. the experts of one MoE layer, or the

@@ -189,6 +189,47 @@ class ExpertParallelMoE:
 
         self.local = {e: dict(gate_up=put(experts[e]["gate_up"]), down=put(experts[e]["down"])) for e in range(first, first + count)}
         self.linear_fn = linear_fn or _default_linear()
+        self._tables = None
+
+    def _address_tables(self, dev):
+        """int64 device tensors [local experts] with the addresses of each expert's wire tensors (for the grouped kernel)."""
+        if self._tables is None:
+            def col(which, i):
+                return torch.tensor([self.local[e][which][i].data_ptr() for e in range(self.first, self.first + self.count)],
+                                    dtype=torch.int64, device=dev)
+            self._tables = {w: tuple(col(w, i) for i in range(4)) for w in ("gate_up", "down")}
+        return self._tables
+
+    def partial_grouped(self, x, topk_ids, topk_w):
+        """The same contribution with two grouped launches (gate_up, down) over all (token, slot) pairs.  Routing stays on
+        the device (no host round trip, capturable in a CUDA graph); needs every routed expert to be local."""
+        from . import ops
+
+        T, hdim = x.shape
+        k = topk_ids.shape[1]
+        P = T * k
+        dev = x.device
+        tabs = self._address_tables(dev)
+        e_idx = (topk_ids.to(dev).reshape(-1) - self.first).to(torch.int64)
+        gq, gs, gu_, gv = (t.index_select(0, e_idx) for t in tabs["gate_up"])
+        dq, ds, du, dv = (t.index_select(0, e_idx) for t in tabs["down"])
+        any_e = next(iter(self.local.values()))
+        mt_gu, nt_gu, W = any_e["gate_up"][0].shape
+        mt_dn, nt_dn, _ = any_e["down"][0].shape
+        K = W // 8
+        esz = x.element_size()
+        x = x.contiguous()
+        tok = torch.arange(T, device=dev, dtype=torch.int64).repeat_interleave(k)
+        gu = torch.empty(P, mt_gu * 16, dtype=x.dtype, device=dev)
+        slot = torch.arange(P, device=dev, dtype=torch.int64)
+        ops.linear_grouped(x.data_ptr() + tok * (hdim * esz), gq, gs, gu_, gv, gu.data_ptr() + slot * (mt_gu * 16 * esz),
+                           mt_gu, nt_gu, K, x.dtype)
+        inter = mt_gu * 8
+        act = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
+        dn = torch.empty(P, mt_dn * 16, dtype=x.dtype, device=dev)
+        ops.linear_grouped(act.data_ptr() + slot * (inter * esz), dq, ds, du, dv, dn.data_ptr() + slot * (mt_dn * 16 * esz),
+                           mt_dn, nt_dn, K, x.dtype)
+        return (dn.view(T, k, -1).float() * topk_w.to(device=dev, dtype=torch.float32)[:, :, None]).sum(1)
 
     def partial(self, x, topk_ids, topk_w):
         """Contribution of this rank's experts, float32 [T, h].  Routing is resolved on the host."""
@@ -208,8 +249,9 @@ class ExpertParallelMoE:
             out.index_add_(0, tok, d.float() * w[:, None])
         return out
 
-    def __call__(self, x, topk_ids, topk_w):
-        part = self.partial(x, topk_ids, topk_w)
+    def __call__(self, x, topk_ids, topk_w, grouped=None):
+        use_grouped = (self.world == 1 and x.is_cuda) if grouped is None else grouped
+        part = self.partial_grouped(x, topk_ids, topk_w) if use_grouped else self.partial(x, topk_ids, topk_w)
         if self.world == 1:
             return part.to(x.dtype)
         g = all_gather_rows(part, self.group)                                # [world, T, h] float32

@@ -93,6 +93,16 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
                      void* const* peer_y, int npeer, int64_t peer_offset, void* workspace, size_t workspace_bytes,
                      htr_stream_t stream, unsigned flags);
 
+/* Grouped form of htr_linear: `count` packed linears of one shape [m, n] and width K, one activation row each, in ONE launch
+ * (the experts hit by the tokens of a mixture-of-experts step).  Every list is a DEVICE array of `count` device pointers
+ * (x_list[i] -> n activations, y_list[i] -> m outputs, and the four wire tensors of problem i), so that a routing kernel can
+ * fill them without a host round trip; the same expert may appear several times.  count * m/128 must not exceed 16384.
+ * (No counterpart in the reference, which ships no MoE runtime kernel: docs/ADAPTERS.md:19.) */
+size_t htr_linear_grouped_workspace_bytes(int count, int m, int n, int K);
+int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* qweight_list, int mt, int nt, int K,
+                       const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list,
+                       void* const* y_list, int count, void* workspace, size_t workspace_bytes, htr_stream_t stream);
+
 /* htr_linear without a workspace argument, for callers that cannot allocate device memory when they need the
  * linear (stream capture in progress, allocation-free real-time loops, hosts whose allocator is not theirs to call).
  * The scratch is a fixed array of HTR_STATIC_WORKSPACE_BYTES inside the library image, held by every GPU that

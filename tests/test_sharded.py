@@ -137,9 +137,16 @@ def test_single_rank_paths_on_gpu(coracle):
     assert torch.equal(lin(x), ops.linear(x, qw, sc, su, sv))
     experts, xm, ids, w = _moe_inputs(E=8, h=256, inter=128, T=6, k=2, K=3, seed=4)
     moe = ExpertParallelMoE(experts, device=dev)
-    y = moe(xm.to(dev), ids, w).float().cpu()
     want = _moe_reference(experts, xm, ids, w, _oracle_linear())
-    assert float((y - want).norm() / want.norm()) <= 1e-5
+    y_loop = moe(xm.to(dev), ids, w, grouped=False).float().cpu()            # host-routed, one call per expert
+    y_grp = moe(xm.to(dev), ids, w, grouped=True).float().cpu()              # two grouped launches, routing on the device
+    assert float((y_loop - want).norm() / want.norm()) <= 1e-5
+    assert float((y_grp - want).norm() / want.norm()) <= 1e-5
+    # bf16 tokens through the grouped path, several tokens hitting the same expert
+    xb = xm.bfloat16()
+    yb = moe(xb.to(dev), ids, w, grouped=True).float().cpu()
+    wantb = _moe_reference(experts, xb, ids, w, _oracle_linear())
+    assert float((yb - wantb).norm() / wantb.norm()) <= 1e-2
 
 
 def _nccl_worker(rank, world, port, q):
