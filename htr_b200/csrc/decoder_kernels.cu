@@ -1,0 +1,209 @@
+// Small fused kernels of the decoder harness (the non-linear glue between packed linears in a decode step):
+// residual add + RMSNorm, rotary embedding + KV-cache write, single-query grouped-query attention, SwiGLU.
+// They exist so that a decode step is a short chain of launches around the packed GEMVs instead of dozens of
+// framework kernels; every one is launched with programmatic stream serialisation, signals its dependents at once and
+// waits for its predecessor before touching data, so the next packed GEMV prefetches its weights while these run.
+// bf16 activations, float32 arithmetic.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/htr_b200.h"
+
+namespace {
+
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ float bf(const __nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = -3.0e38f;
+  for (int i = 0; i < nw; ++i) t = fmaxf(t, red[i]);
+  return t;
+}
+
+// resid += delta (if any); out = rmsnorm(resid) * w.  One CTA per row.
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ resid, const __nv_bfloat16* __restrict__ delta,
+                                                          const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int h, float eps) {
+  __shared__ float red[8];
+  pdl_enter();
+  const size_t row = (size_t)blockIdx.x * h;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 2; i < h; i += 512) {
+    float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(resid + row + i));
+    if (delta) {
+      const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(delta + row + i));
+      v.x += d.x; v.y += d.y;
+      const __nv_bfloat162 r = __floats2bfloat162_rn(v.x, v.y);
+      *reinterpret_cast<__nv_bfloat162*>(resid + row + i) = r;
+      v = __bfloat1622float2(r);                        // the norm sees the stored (rounded) residual, as a framework would
+    }
+    ss += v.x * v.x + v.y * v.y;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)h + eps);
+  for (int i = threadIdx.x * 2; i < h; i += 512) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(resid + row + i));
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + i));
+    // normalise, round to bf16, then scale: the order of the unfused reference ops
+    const __nv_bfloat162 nrm = __floats2bfloat162_rn(v.x * inv, v.y * inv);
+    const float2 nf = __bfloat1622float2(nrm);
+    *reinterpret_cast<__nv_bfloat162*>(out + row + i) = __floats2bfloat162_rn(nf.x * g.x, nf.y * g.y);
+  }
+}
+
+// rotary embedding of q and k (interleaved pairs), k and v written into the cache rows pos[t].  grid (heads_q + 2*heads_kv, T), D/2 threads.
+__global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ pos, const float* __restrict__ cosv,
+                                  const float* __restrict__ sinv, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
+                                  __nv_bfloat16* __restrict__ v_cache, int hq, int hkv, int D) {
+  pdl_enter();
+  const int head = blockIdx.x, t = blockIdx.y, i = threadIdx.x;           // pair index i: elements 2i, 2i+1
+  const long long p = pos[t];
+  const size_t row = (size_t)t * (hq + 2 * hkv) * D;
+  const __nv_bfloat162 in = *reinterpret_cast<const __nv_bfloat162*>(qkv + row + (size_t)head * D + 2 * i);
+  if (head >= hq + hkv) {                                                 // v: plain copy into the cache
+    *reinterpret_cast<__nv_bfloat162*>(v_cache + ((size_t)p * hkv + (head - hq - hkv)) * D + 2 * i) = in;
+    return;
+  }
+  const float2 v = __bfloat1622float2(in);
+  const float c = cosv[(size_t)p * (D / 2) + i], s = sinv[(size_t)p * (D / 2) + i];
+  const __nv_bfloat162 r = __floats2bfloat162_rn(v.x * c - v.y * s, v.x * s + v.y * c);
+  if (head < hq) *reinterpret_cast<__nv_bfloat162*>(q_out + ((size_t)t * hq + head) * D + 2 * i) = r;
+  else *reinterpret_cast<__nv_bfloat162*>(k_cache + ((size_t)p * hkv + (head - hq)) * D + 2 * i) = r;
+}
+
+// out[t, head, :] = softmax(q . K[0..pos[t]] / sqrt(D)) V.  grid (heads_q, T), 128 threads, D == 128, positions <= HTR_DEC_MAX_LEN.
+__global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                                                        const __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ pos,
+                                                        __nv_bfloat16* __restrict__ out, int hq, int hkv) {
+  constexpr int D = 128;
+  __shared__ float sq[D];
+  __shared__ float sc[HTR_DEC_MAX_LEN];
+  __shared__ float red[4];
+  pdl_enter();
+  const int head = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int kvh = head / (hq / hkv);
+  const int len = (int)pos[t] + 1;
+  sq[tid] = bf(q[((size_t)t * hq + head) * D + tid]) * 0.08838834764831845f;   // 1/sqrt(128)
+  __syncthreads();
+  // scores: one warp per position, four dimensions per lane
+  float mx = -3.0e38f;
+  for (int p = warp; p < len; p += 4) {
+    const __nv_bfloat16* kr = k_cache + ((size_t)p * hkv + kvh) * D + 4 * lane;
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kr)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kr + 2));
+    float d = a.x * sq[4 * lane] + a.y * sq[4 * lane + 1] + b.x * sq[4 * lane + 2] + b.y * sq[4 * lane + 3];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
+    if (lane == 0) sc[p] = d;
+    mx = fmaxf(mx, d);
+  }
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int p = tid; p < len; p += 128) {
+    const float e = __expf(sc[p] - mx);
+    sc[p] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  // weighted values: thread = dimension
+  float acc = 0.f;
+  for (int p = 0; p < len; ++p) acc += sc[p] * bf(v_cache[((size_t)p * hkv + kvh) * D + tid]);
+  out[((size_t)t * hq + head) * D + tid] = __float2bfloat16_rn(acc / sum);
+}
+
+// out = silu(gate) * up, gu = [T, 2I] with the gate half first
+__global__ void __launch_bounds__(256) swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, int total) {
+  pdl_enter();
+  const int idx = (blockIdx.x * 256 + threadIdx.x) * 2;
+  if (idx >= total) return;
+  const int t = idx / I, j = idx - t * I;
+  const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + (size_t)t * 2 * I + j));
+  const float2 u = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gu + (size_t)t * 2 * I + I + j));
+  // silu rounded to bf16 before the product, as the unfused ops do
+  const __nv_bfloat162 s = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)), g.y / (1.f + __expf(-g.y)));
+  const float2 sf = __bfloat1622float2(s);
+  *reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * I + j) = __floats2bfloat162_rn(sf.x * u.x, sf.y * u.y);
+}
+
+template <typename Kern, typename... Args>
+int launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+}  // namespace
+
+extern "C" {
+
+int htr_dec_add_rmsnorm(void* resid, const void* delta, const void* weight, void* out, int rows, int h, float eps, htr_stream_t stream) {
+  if (rows <= 0) return HTR_OK;
+  if (!resid || !weight || !out) return HTR_ERR_NULL;
+  if (h <= 0 || h % 2) return HTR_ERR_BAD_SHAPE;
+  const int e = launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(256), static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16*>(resid),
+                           static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), h, eps);
+  return e ? HTR_ERR_CUDA : HTR_OK;
+}
+
+int htr_dec_rope_cache(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* q_out, void* k_cache, void* v_cache,
+                       int rows, int q_heads, int kv_heads, int head_dim, htr_stream_t stream) {
+  if (rows <= 0) return HTR_OK;
+  if (!qkv || !pos || !cosv || !sinv || !q_out || !k_cache || !v_cache) return HTR_ERR_NULL;
+  if (head_dim <= 0 || head_dim % 2 || head_dim > 2048 || q_heads <= 0 || kv_heads <= 0) return HTR_ERR_BAD_SHAPE;
+  const int e = launch_pdl(rope_cache_kernel, dim3(q_heads + 2 * kv_heads, rows), dim3(head_dim / 2), static_cast<cudaStream_t>(stream),
+                           static_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const long long*>(pos), cosv, sinv,
+                           static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), q_heads,
+                           kv_heads, head_dim);
+  return e ? HTR_ERR_CUDA : HTR_OK;
+}
+
+int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int rows, int q_heads,
+                      int kv_heads, int head_dim, htr_stream_t stream) {
+  if (rows <= 0) return HTR_OK;
+  if (!q || !k_cache || !v_cache || !pos || !out) return HTR_ERR_NULL;
+  if (head_dim != 128 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return HTR_ERR_BAD_SHAPE;
+  const int e = launch_pdl(attention_kernel, dim3(q_heads, rows), dim3(128), static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(q),
+                           static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
+                           reinterpret_cast<const long long*>(pos), static_cast<__nv_bfloat16*>(out), q_heads, kv_heads);
+  return e ? HTR_ERR_CUDA : HTR_OK;
+}
+
+int htr_dec_swiglu(const void* gate_up, void* out, int rows, int intermediate, htr_stream_t stream) {
+  if (rows <= 0) return HTR_OK;
+  if (!gate_up || !out) return HTR_ERR_NULL;
+  if (intermediate <= 0 || intermediate % 2) return HTR_ERR_BAD_SHAPE;
+  const int total = rows * intermediate;
+  const int e = launch_pdl(swiglu_kernel, dim3((total / 2 + 255) / 256), dim3(256), static_cast<cudaStream_t>(stream),
+                           static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), intermediate, total);
+  return e ? HTR_ERR_CUDA : HTR_OK;
+}
+
+}  // extern "C"

@@ -6,16 +6,18 @@ the reference's headline case: a 9B-class dense decoder (36 layers, hidden 4096,
 decoding (docs/case-studies/dense-9b.md of the reference).  Weights are random (no checkpoint is available); fused
 projections (q|k|v, gate|up) are single packed linears, as the format prescribes (docs/FORMAT.md:31-32).
 
-Every packed linear goes through `htr_b200.ops.linear`; the rest (RMSNorm, rotary embedding, attention over a static
-KV cache, SwiGLU) are plain torch ops.  A decode step reads its position from a device tensor, so one CUDA graph
-captured once serves every step.
+Every packed linear goes through `htr_b200.ops.linear`.  The glue between them (residual add + RMSNorm, rotary embedding
++ KV-cache write, single-query grouped attention, SwiGLU) runs as four small fused kernels of the library
+(`htr_dec_*`, launched with programmatic stream serialisation so the following packed GEMV prefetches its weights while
+they run); `fused=False` evaluates the same glue with plain torch ops, which is how the kernels are checked.  A decode
+step reads its position from a device tensor, so one CUDA graph captured once serves every step.
 """
 import dataclasses
 import math
 
 import torch
 
-from . import ops, wire
+from . import _lib, ops, wire
 
 
 @dataclasses.dataclass
@@ -40,8 +42,9 @@ def _rms_norm(x, w, eps):
 
 
 class PackedDecoder:
-    def __init__(self, cfg, device, seed=0, dtype=torch.bfloat16):
-        self.cfg, self.device, self.dtype = cfg, device, dtype
+    def __init__(self, cfg, device, seed=0, dtype=torch.bfloat16, fused=True):
+        self.cfg, self.device, self.dtype, self.fused = cfg, device, dtype, fused
+        assert cfg.max_len <= 1024, "the attention glue kernel holds at most 1024 positions"
         g = torch.Generator().manual_seed(seed)
         c = cfg
         qkv_out = (c.q_heads + 2 * c.kv_heads) * c.head_dim
@@ -79,9 +82,42 @@ class PackedDecoder:
         out = torch.stack((t1 * cos - t2 * sin, t1 * sin + t2 * cos), dim=-1)
         return out.flatten(-2).to(t.dtype)
 
+    def forward_fused(self, ids, pos):
+        """The same step with the library's glue kernels (bf16 only)."""
+        c, L_ = self.cfg, _lib.lib
+        T = ids.shape[0]
+        dev = self.device
+        st = torch.cuda.current_stream(dev).cuda_stream
+        x = self.embed.index_select(0, ids)                     # residual stream, updated in place
+        h = torch.empty_like(x)
+        q = torch.empty(T, c.q_heads, c.head_dim, dtype=self.dtype, device=dev)
+        att = torch.empty_like(q)
+        act = torch.empty(T, c.intermediate, dtype=self.dtype, device=dev)
+        delta = None
+        for li, L in enumerate(self.layers):
+            _lib.check(L_.htr_dec_add_rmsnorm(x.data_ptr(), None if delta is None else delta.data_ptr(), L["ln1"].data_ptr(), h.data_ptr(),
+                                              T, c.hidden, c.eps, st), "htr_dec_add_rmsnorm")
+            qkv = ops.linear(h, *L["qkv"])
+            _lib.check(L_.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), q.data_ptr(),
+                                             self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st),
+                       "htr_dec_rope_cache")
+            _lib.check(L_.htr_dec_attention(q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), pos.data_ptr(),
+                                            att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_attention")
+            o = ops.linear(att.view(T, c.q_heads * c.head_dim), *L["o"])
+            _lib.check(L_.htr_dec_add_rmsnorm(x.data_ptr(), o.data_ptr(), L["ln2"].data_ptr(), h.data_ptr(), T, c.hidden, c.eps, st),
+                       "htr_dec_add_rmsnorm")
+            gu = ops.linear(h, *L["gate_up"])
+            _lib.check(L_.htr_dec_swiglu(gu.data_ptr(), act.data_ptr(), T, c.intermediate, st), "htr_dec_swiglu")
+            delta = ops.linear(act, *L["down"])
+        _lib.check(L_.htr_dec_add_rmsnorm(x.data_ptr(), delta.data_ptr(), self.ln_f.data_ptr(), h.data_ptr(), T, c.hidden, c.eps, st),
+                   "htr_dec_add_rmsnorm")
+        return ops.linear(h, *self.head)
+
     def forward(self, ids, pos):
         """ids [T] token ids, pos [T] their positions (device tensors).  Returns logits [T, vocab] and updates the cache."""
         c = self.cfg
+        if self.fused and self.dtype == torch.bfloat16 and c.head_dim == 128:
+            return self.forward_fused(ids, pos)
         T = ids.shape[0]
         x = self.embed.index_select(0, ids)
         # a query at position p sees cache slots <= p

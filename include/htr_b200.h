@@ -136,6 +136,23 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
 int htr_dequant_w(const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su, const uint8_t* sv,
                   void* W, int out_dtype, htr_stream_t stream);
 
+/* Glue kernels of the decoder harness (bf16 tensors, float32 arithmetic), all asynchronous on `stream`.  They stand in for
+ * the framework ops a serving stack runs between the packed linears of a decode step (the model code around
+ * HTRLinearMethod.apply, htr/vllm_plugin.py:130-138); the reference ships none of its own.
+ *   add_rmsnorm : resid[rows,h] += delta (delta may be NULL); out = rmsnorm(resid, eps) * weight
+ *   rope_cache  : rotary embedding (interleaved pairs) of the q and k parts of qkv[rows, (q_heads+2*kv_heads)*head_dim];
+ *                 q -> q_out[rows,q_heads,head_dim]; k, v -> cache rows pos[row] of k_cache/v_cache[max_len,kv_heads,head_dim]
+ *   attention   : out[row,head,:] = softmax(q . K[0..pos[row]] / sqrt(head_dim)) V, grouped-query, head_dim == 128,
+ *                 pos[row] < HTR_DEC_MAX_LEN
+ *   swiglu      : out[rows,I] = silu(gate_up[:, :I]) * gate_up[:, I:] */
+#define HTR_DEC_MAX_LEN 1024
+int htr_dec_add_rmsnorm(void* resid, const void* delta, const void* weight, void* out, int rows, int h, float eps, htr_stream_t stream);
+int htr_dec_rope_cache(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* q_out, void* k_cache,
+                       void* v_cache, int rows, int q_heads, int kv_heads, int head_dim, htr_stream_t stream);
+int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int rows, int q_heads,
+                      int kv_heads, int head_dim, htr_stream_t stream);
+int htr_dec_swiglu(const void* gate_up, void* out, int rows, int intermediate, htr_stream_t stream);
+
 /* Launch-shape knobs of htr_linear for measurements (0 = library default): CTAs per SM of the GEMV grid. */
 void htr_set_gemv_ctas_per_sm(int ctas);
 /* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */

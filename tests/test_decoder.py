@@ -11,7 +11,17 @@ def test_small_decoder_matches_dense_evaluation():
     from htr_b200.decoder import DecoderConfig, PackedDecoder, _rms_norm
 
     dev = torch.device("cuda:0")
-    cfg = DecoderConfig(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=64, intermediate=512, vocab=1024, K=4, K_head=4, max_len=64)
+    cfg = DecoderConfig(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, intermediate=512, vocab=1024, K=4, K_head=4, max_len=64)
+    model = PackedDecoder(cfg, dev, seed=3)
+    # the fused glue kernels reproduce the plain torch ops: same logits for a prompt pass and a single-token step
+    plain = PackedDecoder(cfg, dev, seed=3, fused=False)
+    ids9 = torch.randint(0, cfg.vocab, (9,), generator=torch.Generator().manual_seed(5)).to(dev)
+    lf, lp = model.forward(ids9, torch.arange(9, device=dev)), plain.forward(ids9, torch.arange(9, device=dev))
+    assert float((lf.float() - lp.float()).norm() / lp.float().norm()) <= 2e-2
+    one, at = ids9[:1], torch.full((1,), 9, device=dev, dtype=torch.long)
+    lf1, lp1 = model.forward(one, at), plain.forward(one, at)
+    assert float((lf1.float() - lp1.float()).norm() / lp1.float().norm()) <= 2e-2
+    assert torch.allclose(model.k_cache.float(), plain.k_cache.float(), atol=2e-2) and torch.allclose(model.v_cache.float(), plain.v_cache.float(), atol=2e-2)
     model = PackedDecoder(cfg, dev, seed=3)
     prompt = torch.randint(0, cfg.vocab, (9,), generator=torch.Generator().manual_seed(1))
     toks, t_prompt, t_decode = model.generate(prompt, 12, use_graph=True)
