@@ -44,32 +44,43 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   return t;
 }
 
-// resid += delta (if any); out = rmsnorm(resid) * w.  One CTA per row.
+// resid += delta (if any); out = rmsnorm(resid) * w.  One CTA per row; the row stays in registers between the two passes
+// (h <= 8192: up to 16 bf16 pairs per thread).
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restrict__ resid, const __nv_bfloat16* __restrict__ delta,
                                                           const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int h, float eps) {
   __shared__ float red[8];
   pdl_enter();
   const size_t row = (size_t)blockIdx.x * h;
+  constexpr int kMaxPairs = 16;
+  float2 v[kMaxPairs];
+  float2 g[kMaxPairs];
   float ss = 0.f;
-  for (int i = threadIdx.x * 2; i < h; i += 512) {
-    float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(resid + row + i));
-    if (delta) {
-      const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(delta + row + i));
-      v.x += d.x; v.y += d.y;
-      const __nv_bfloat162 r = __floats2bfloat162_rn(v.x, v.y);
-      *reinterpret_cast<__nv_bfloat162*>(resid + row + i) = r;
-      v = __bfloat1622float2(r);                        // the norm sees the stored (rounded) residual, as a framework would
+#pragma unroll
+  for (int j = 0; j < kMaxPairs; ++j) {
+    const int i = (threadIdx.x + j * 256) * 2;
+    v[j] = make_float2(0.f, 0.f);
+    g[j] = make_float2(0.f, 0.f);
+    if (i < h) {
+      v[j] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(resid + row + i));
+      g[j] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + i));
+      if (delta) {
+        const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(delta + row + i));
+        const __nv_bfloat162 r = __floats2bfloat162_rn(v[j].x + d.x, v[j].y + d.y);
+        *reinterpret_cast<__nv_bfloat162*>(resid + row + i) = r;
+        v[j] = __bfloat1622float2(r);                   // the norm sees the stored (rounded) residual, as a framework would
+      }
+      ss += v[j].x * v[j].x + v[j].y * v[j].y;
     }
-    ss += v.x * v.x + v.y * v.y;
   }
   const float inv = rsqrtf(block_sum(ss, red) / (float)h + eps);
-  for (int i = threadIdx.x * 2; i < h; i += 512) {
-    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(resid + row + i));
-    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + i));
-    // normalise, round to bf16, then scale: the order of the unfused reference ops
-    const __nv_bfloat162 nrm = __floats2bfloat162_rn(v.x * inv, v.y * inv);
-    const float2 nf = __bfloat1622float2(nrm);
-    *reinterpret_cast<__nv_bfloat162*>(out + row + i) = __floats2bfloat162_rn(nf.x * g.x, nf.y * g.y);
+#pragma unroll
+  for (int j = 0; j < kMaxPairs; ++j) {
+    const int i = (threadIdx.x + j * 256) * 2;
+    if (i < h) {
+      // normalise, round to bf16, then scale: the order of the unfused reference ops
+      const float2 nf = __bfloat1622float2(__floats2bfloat162_rn(v[j].x * inv, v[j].y * inv));
+      *reinterpret_cast<__nv_bfloat162*>(out + row + i) = __floats2bfloat162_rn(nf.x * g[j].x, nf.y * g[j].y);
+    }
   }
 }
 
@@ -94,28 +105,34 @@ __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const l
 }
 
 // out[t, head, :] = softmax(q . K[0..pos[t]] / sqrt(D)) V.  grid (heads_q, T), 128 threads, D == 128, positions <= HTR_DEC_MAX_LEN.
+// Scores: one thread per position (128 positions per pass, the 256-byte key row read as sixteen 16-byte loads);
+// values: one thread per dimension, eight positions in flight.
 __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                                                         const __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ pos,
                                                         __nv_bfloat16* __restrict__ out, int hq, int hkv) {
   constexpr int D = 128;
-  __shared__ float sq[D];
+  __shared__ __align__(16) float sq[D];
   __shared__ float sc[HTR_DEC_MAX_LEN];
   __shared__ float red[4];
   pdl_enter();
-  const int head = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int head = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
   const int kvh = head / (hq / hkv);
   const int len = (int)pos[t] + 1;
   sq[tid] = bf(q[((size_t)t * hq + head) * D + tid]) * 0.08838834764831845f;   // 1/sqrt(128)
   __syncthreads();
-  // scores: one warp per position, four dimensions per lane
   float mx = -3.0e38f;
-  for (int p = warp; p < len; p += 4) {
-    const __nv_bfloat16* kr = k_cache + ((size_t)p * hkv + kvh) * D + 4 * lane;
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kr)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(kr + 2));
-    float d = a.x * sq[4 * lane] + a.y * sq[4 * lane + 1] + b.x * sq[4 * lane + 2] + b.y * sq[4 * lane + 3];
+  for (int p = tid; p < len; p += 128) {
+    const uint4* kr = reinterpret_cast<const uint4*>(k_cache + ((size_t)p * hkv + kvh) * D);
+    float d = 0.f;
 #pragma unroll
-    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
-    if (lane == 0) sc[p] = d;
+    for (int c = 0; c < 16; ++c) {
+      const uint4 raw = __ldg(kr + c);
+      const float4 q0 = *reinterpret_cast<const float4*>(sq + 8 * c), q1 = *reinterpret_cast<const float4*>(sq + 8 * c + 4);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z)), f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+      d += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + e.x * q1.x + e.y * q1.y + f.x * q1.z + f.y * q1.w;
+    }
+    sc[p] = d;
     mx = fmaxf(mx, d);
   }
   mx = block_max(mx, red);
@@ -126,9 +143,17 @@ __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __r
     sum += e;
   }
   sum = block_sum(sum, red);
-  // weighted values: thread = dimension
+  const __nv_bfloat16* vcol = v_cache + (size_t)kvh * D + tid;
   float acc = 0.f;
-  for (int p = 0; p < len; ++p) acc += sc[p] * bf(v_cache[((size_t)p * hkv + kvh) * D + tid]);
+  int p = 0;
+  for (; p + 8 <= len; p += 8) {
+    float vv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vv[j] = bf(vcol[(size_t)(p + j) * hkv * D]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += sc[p + j] * vv[j];
+  }
+  for (; p < len; ++p) acc += sc[p] * bf(vcol[(size_t)p * hkv * D]);
   out[((size_t)t * hq + head) * D + tid] = __float2bfloat16_rn(acc / sum);
 }
 
@@ -167,7 +192,7 @@ extern "C" {
 int htr_dec_add_rmsnorm(void* resid, const void* delta, const void* weight, void* out, int rows, int h, float eps, htr_stream_t stream) {
   if (rows <= 0) return HTR_OK;
   if (!resid || !weight || !out) return HTR_ERR_NULL;
-  if (h <= 0 || h % 2) return HTR_ERR_BAD_SHAPE;
+  if (h <= 0 || h % 2 || h > 8192) return HTR_ERR_BAD_SHAPE;
   const int e = launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(256), static_cast<cudaStream_t>(stream), static_cast<__nv_bfloat16*>(resid),
                            static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(out), h, eps);
   return e ? HTR_ERR_CUDA : HTR_OK;
