@@ -11,8 +11,8 @@ LIB_PATH = os.environ.get("HTR_B200_LIB") or os.path.join(_HERE, "libhtr_b200.so
 
 BF16, F16, F32 = 0, 1, 2
 GEMV_MAX_ROWS = 8
-GEMM_MAX_ROWS = 128
-GEMM_MAX_ROWS_F32 = 64
+GEMM_MAX_ROWS = 256
+GEMM_MAX_ROWS_F32 = 128
 INPUT_INDEPENDENT = 1
 
 EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
@@ -70,5 +70,6 @@ def check(status, what):
     if status != 0:
         msg = lib.htr_status_string(status).decode()
         if status == -7:
-            msg += f" (cudaError {lib.htr_last_cuda_error()})"
+            code = lib.htr_linear_gemm_last_cuda_error() if what.startswith("htr_linear_gemm") else lib.htr_last_cuda_error()
+            msg += f" (cudaError {code})"
         raise HTRError(f"{what}: {msg}")

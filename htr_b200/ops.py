@@ -7,9 +7,9 @@ for one B200 (148 SMs, HBM3e) rather than copied from the 40-CU part the referen
   M == 0            empty result                                             (htr/ops.py:73-74)
   1 <= M <= 8       one launch of the streaming GEMV (activation transform, decode + dot, split reduce,
                     output transform fused)                                  (replaces htr/ops.py:75-76,95-101)
-  8 < M <= 128      the tensor-core packed GEMM (tcgen05 + TMEM); decoded tiles go straight into the MMA operand
-                                                                             (replaces htr/ops.py:77-93)
-  M > 128           original-basis bf16 weight from the dequant kernel (decoded once), then a library GEMM
+  8 < M <= 512      the tensor-core packed GEMM (tcgen05 + TMEM), up to 256 rows per launch (128 for float32
+                    activations); decoded tiles go straight into the MMA operand    (replaces htr/ops.py:77-93)
+  M > 512           original-basis bf16 weight from the dequant kernel (decoded once), then a library GEMM
                                                                              (htr/ops.py:89-93)
   HTR_GEMM=0        instead: GEMV over 8-row chunks up to HTR_GEMV_LOOP_MAX rows, beyond that the original-basis bf16
                     weight from the dequant kernel + a library GEMM (the reference's own routes, kept for comparison)
@@ -28,8 +28,8 @@ GEMV_MAX_M = _lib.GEMV_MAX_ROWS
 GEMV_LOOP_MAX = int(os.environ.get("HTR_GEMV_LOOP_MAX", "64"))
 USE_GEMM = os.environ.get("HTR_GEMM", "1") == "1"
 GEMM_MAX_M = _lib.GEMM_MAX_ROWS
-# above this many rows the weight is decoded once to bf16 and a library GEMM runs (the packed GEMM decodes per 128-row chunk)
-GEMM_ROUTE_MAX = int(os.environ.get("HTR_GEMM_ROUTE_MAX", "128"))
+# above this many rows the weight is decoded once to bf16 and a library GEMM runs (the packed GEMM decodes once per 256-row launch)
+GEMM_ROUTE_MAX = int(os.environ.get("HTR_GEMM_ROUTE_MAX", "512"))
 
 _FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
 
@@ -97,7 +97,7 @@ _GEMM_WS = {}
 
 
 def _gemm(x2, qweight, scales, su, sv, bias, out):
-    """One C call of the tensor-core GEMM: up to 128 rows of x2 against the packed weight."""
+    """One C call of the tensor-core GEMM: up to 256 rows of x2 (128 for float32) against the packed weight."""
     M = x2.shape[0]
     mt, nt, W = qweight.shape
     K = W // 8

@@ -121,8 +121,8 @@ int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int 
  * The workspace starts with the same zero-initialised counter region as htr_linear's, followed by one status word at
  * htr_linear_gemm_error_offset(): non-zero after a call means a bounded device-side wait expired and the output is
  * invalid.  Stands in for the prefill branch of _linear_impl, dequant_w + F.linear (htr/ops.py:89-93). */
-#define HTR_GEMM_MAX_ROWS 128
-#define HTR_GEMM_MAX_ROWS_F32 64 /* float32 activations travel as two fp16 planes: half as many rows per call */
+#define HTR_GEMM_MAX_ROWS 256
+#define HTR_GEMM_MAX_ROWS_F32 128 /* float32 activations travel as two fp16 planes: half as many rows per call */
 size_t htr_linear_gemm_workspace_bytes(int M, int m, int n, int K);
 size_t htr_linear_gemm_error_offset(void);
 int htr_linear_gemm_last_cuda_error(void);

@@ -14,7 +14,7 @@ def rel(a, b):
 
 
 @pytest.mark.parametrize("K", (2, 3, 4, 5, 6, 8))
-@pytest.mark.parametrize("m,n,M", ((128, 128, 16), (256, 1024, 9), (384, 512, 33), (128, 2048, 64), (512, 256, 128), (256, 384, 100)))
+@pytest.mark.parametrize("m,n,M", ((128, 128, 16), (256, 1024, 9), (384, 512, 33), (128, 2048, 64), (512, 256, 128), (256, 384, 100), (256, 256, 256), (128, 640, 200), (128, 256, 300)))
 def test_gemm_matches_oracle(coracle, K, m, n, M):
     from htr_b200 import ops, wire
 
