@@ -470,6 +470,25 @@ def run_extra(args):
         dist.destroy_process_group()
 
 
+def run_case(spec):
+    """A small fixed case for a profiler: `copies` random packed linears of one shape (more than L2 in total when the shape
+    allows), each called once per repetition through `ops.linear`, eagerly.  spec: K=4,m=4096,n=12288,M=64[,copies=6,reps=1,dtype=bf16]"""
+    import torch
+    from htr_b200 import ops, wire
+    kv = dict(item.split("=") for item in spec.split(","))
+    K, m, n, M = int(kv["K"]), int(kv["m"]), int(kv["n"]), int(kv["M"])
+    copies, reps = int(kv.get("copies", 6)), int(kv.get("reps", 1))
+    dtype = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[kv.get("dtype", "bf16")]
+    dev = torch.device("cuda:0")
+    ws = [wire.random_packed(m, n, K, seed=s, device=dev) for s in range(copies)]
+    x = torch.randn(M, n, device=dev).to(dtype)
+    for _ in range(reps):
+        for w in ws:
+            ops.linear(x, *w)
+    torch.cuda.synchronize()
+    print(json.dumps({"case": spec, "launches": copies * reps, "gemm_errors": ops.gemm_error_codes()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -480,8 +499,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--workload", default="mlp", choices=("mlp", "lmhead", "decoder", "moe"),
                     help="mlp = the default benchmark line; the others print lines for the remaining configurations")
+    ap.add_argument("--case", default=None, help="run one small fixed case for a profiler and exit, e.g. K=4,m=4096,n=12288,M=64")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args.case)
+    elif args.impl == "reference":
         run_reference(args)
     elif args.workload != "mlp":
         run_extra(args)
