@@ -126,6 +126,11 @@ using namespace htr;
 
 extern "C" {
 
+static int launch_linear(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
+                         const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
+                         int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags);
+
+
 const char* htr_status_string(int status) {
   switch (status) {
     case HTR_OK: return "ok";
@@ -200,6 +205,23 @@ int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, 
 int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
                      const uint8_t* sv, const void* bias, void* y, void* const* peer_y, int npeer, int64_t peer_offset, void* workspace,
                      size_t workspace_bytes, htr_stream_t stream, unsigned flags) {
+  return launch_linear(x, dtype, M, nt * 16, qweight, mt, nt, K, scales, su, sv, bias, y, mt * 16, peer_y, npeer, peer_offset, workspace,
+                       workspace_bytes, stream, flags);
+}
+
+int htr_linear_padded(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
+                      const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* workspace, size_t workspace_bytes,
+                      htr_stream_t stream) {
+  if (mt <= 0 || nt <= 0) return HTR_ERR_BAD_SHAPE;
+  if (n_in < 8 || n_in > nt * 16 || n_in % 8 || m_out < 8 || m_out > mt * 16 || m_out % 8) return HTR_ERR_BAD_SHAPE;
+  return launch_linear(x, dtype, M, n_in, qweight, mt, nt, K, scales, su, sv, bias, y, m_out, nullptr, 0, 0, workspace, workspace_bytes,
+                       stream, 0u);
+}
+
+// shared body of the single-problem entry points: x has n_in <= n columns (the rest read as zeros), y gets the first m_out <= m rows
+static int launch_linear(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
+                         const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
+                         int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (M < 0 || M > HTR_GEMV_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
@@ -237,6 +259,8 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
   p.units = pl.units;
   p.split = pl.split;
   p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
+  p.n_in = n_in;
+  p.m_out = m_out;
   p.group = 0;
   p.rb_per_problem = 0;
   p.g_x = nullptr; p.g_qw = nullptr; p.g_scales = nullptr; p.g_su = nullptr; p.g_sv = nullptr; p.g_y = nullptr;
@@ -307,6 +331,8 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
   p.independent = 0;
   p.cb = (float)codebook_scale();
   p.npeer = 0;
+  p.n_in = nt * 16;
+  p.m_out = mt * 16;
   p.peer_offset = 0;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
   p.group = count;

@@ -74,6 +74,8 @@ struct GemvParams {
   int split;        // > 0: every row block is shared by exactly `split` CTAs (grid = row blocks * split); 0: flat unit ranges
   int slots;        // partial slots per row block
   int independent;  // 1: x, bias and y are untouched by the preceding kernel of the stream (wait only before publishing)
+  int n_in;         // columns present in x (row stride of x); columns n_in .. n-1 of the stored weight see zeros
+  int m_out;        // rows written to y (row stride of y, length of bias); rows m_out .. m-1 of the stored weight are dropped
   float cb;
   // Peer form (row-sharded linears over NVLink): when npeer > 0 the epilogue writes its rows into every listed buffer
   // (peers' and its own, plain stores through peer-mapped addresses) at element offset peer_offset, instead of into y.
@@ -91,6 +93,11 @@ struct GemvParams {
   const uint8_t* const* g_sv;
   void* const* g_y;         // 1 / rms of the codebook integers
 };
+
+// four consecutive activations of row r at column col (a multiple of 4); columns at or beyond n_in (a multiple of 4) read as zero
+__device__ __forceinline__ float4 load_x(const void* x, int r, int col, int n_in, int dtype) {
+  return col < n_in ? load_quad(x, (size_t)r * n_in + col, dtype) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
 
 // owner CTA of unit x when CTA b starts at floor(b*U/G)
 __device__ __host__ inline int unit_owner(long long x, long long G, long long U) { return (int)(((x + 1) * G - 1) / U); }
@@ -296,7 +303,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     const int items = MT * (hb1 - hb0);
     float4 xv_first = make_float4(0.f, 0.f, 0.f, 0.f);
     if (warp < items && warp / (hb1 - hb0) < p.rows)                // the first item's loads go out before the copy burst
-      xv_first = load_quad(x_ptr, (size_t)(warp / (hb1 - hb0)) * n + (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.dtype);
+      xv_first = load_x(x_ptr, warp / (hb1 - hb0), (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.n_in, p.dtype);
     if (!ring_primed) {
 #pragma unroll
       for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
@@ -306,7 +313,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       const int r = item / (hb1 - hb0), hb = hb0 + item % (hb1 - hb0);
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (r < p.rows) {
-        const float4 xv = item == warp ? xv_first : load_quad(x_ptr, (size_t)r * n + hb * 128 + 4 * lane, p.dtype);
+        const float4 xv = item == warp ? xv_first : load_x(x_ptr, r, hb * 128 + 4 * lane, p.n_in, p.dtype);
         const unsigned sg = sign_nibble(su_ptr, hb * 32 + lane);
         v[0] = flip(xv.x, sg & 1u); v[1] = flip(xv.y, (sg >> 1) & 1u); v[2] = flip(xv.z, (sg >> 2) & 1u); v[3] = flip(xv.w, sg >> 3);
         wht128(v, lane);
@@ -369,7 +376,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     if (warp < p.rows) {
       sc_raw = __ldg(reinterpret_cast<const uint2*>(scales_ptr + row0));
       sv_bits = sign_nibble(sv_ptr, (rb - rb_base) * 32 + lane);
-      if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
+      if (p.bias && row0 < p.m_out) bias4 = load_quad(p.bias, row0, p.dtype);
     }
     if (!predecessor_done) {                           // deferred wait of the independent-input form
       asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -420,7 +427,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
                              flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
       o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
       if (p.npeer == 0) {
-        store_quad(y_ptr, (size_t)r * m + row0, p.dtype, o);
+        if (row0 < p.m_out) store_quad(y_ptr, (size_t)r * p.m_out + row0, p.dtype, o);
       } else {
 #pragma unroll 1
         for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);

@@ -42,9 +42,24 @@ def _rms_norm(x, w, eps):
 
 
 class PackedDecoder:
-    def __init__(self, cfg, device, seed=0, dtype=torch.bfloat16, fused=True):
+    def __init__(self, cfg, device, seed=0, dtype=torch.bfloat16, fused=True, weights=None):
+        """Random packed weights from `seed`, or `weights` = dict(layers=[{qkv, o, gate_up, down, ln1, ln2}], head, ln_f, embed)
+        already on `device` (see from_checkpoint)."""
         self.cfg, self.device, self.dtype, self.fused = cfg, device, dtype, fused
         assert cfg.max_len <= 1024, "the attention glue kernel holds at most 1024 positions"
+        c = cfg
+        if weights is None:
+            weights = self.random_weights(cfg, device, seed, dtype)
+        self.layers, self.head, self.ln_f, self.embed = weights["layers"], weights["head"], weights["ln_f"], weights["embed"]
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2).float() / c.head_dim))
+        ang = torch.arange(c.max_len).float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos().to(device), ang.sin().to(device)
+        self.k_cache = torch.zeros(c.layers, c.max_len, c.kv_heads, c.head_dim, dtype=dtype, device=device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.arange = torch.arange(c.max_len, device=device)
+
+    @staticmethod
+    def random_weights(cfg, device, seed=0, dtype=torch.bfloat16):
         g = torch.Generator().manual_seed(seed)
         c = cfg
         qkv_out = (c.q_heads + 2 * c.kv_heads) * c.head_dim
@@ -52,21 +67,110 @@ class PackedDecoder:
         def packed(m, n, K, s):
             return wire.random_packed(m, n, K, seed=seed * 100003 + s, device=device)
 
-        self.layers = []
+        layers = []
         for i in range(c.layers):
-            self.layers.append(dict(
+            layers.append(dict(
                 qkv=packed(qkv_out, c.hidden, c.K, 10 * i + 1), o=packed(c.hidden, c.q_heads * c.head_dim, c.K, 10 * i + 2),
                 gate_up=packed(2 * c.intermediate, c.hidden, c.K, 10 * i + 3), down=packed(c.hidden, c.intermediate, c.K, 10 * i + 4),
                 ln1=torch.ones(c.hidden, dtype=dtype, device=device), ln2=torch.ones(c.hidden, dtype=dtype, device=device)))
-        self.head = packed(c.vocab, c.hidden, c.K_head, 7)
-        self.ln_f = torch.ones(c.hidden, dtype=dtype, device=device)
-        self.embed = (torch.randn(c.vocab, c.hidden, generator=g) * 0.02).to(dtype).to(device)
-        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2).float() / c.head_dim))
-        ang = torch.arange(c.max_len).float()[:, None] * inv[None, :]
-        self.cos, self.sin = ang.cos().to(device), ang.sin().to(device)
-        self.k_cache = torch.zeros(c.layers, c.max_len, c.kv_heads, c.head_dim, dtype=dtype, device=device)
-        self.v_cache = torch.zeros_like(self.k_cache)
-        self.arange = torch.arange(c.max_len, device=device)
+        return dict(layers=layers, head=packed(c.vocab, c.hidden, c.K_head, 7), ln_f=torch.ones(c.hidden, dtype=dtype, device=device),
+                    embed=(torch.randn(c.vocab, c.hidden, generator=g) * 0.02).to(dtype).to(device))
+
+    # ---- checkpoints in the reference converter's layout (htr_b200/checkpoint.py) ----------------------------------
+    def export_checkpoint(self, out_dir, shards=2):
+        """Writes this model as a packed checkpoint: fused projections are stored per member (q/k/v, gate/up), as the
+        reference's converter stores them (htr/quantize.py:252-289)."""
+        from . import checkpoint
+
+        c = self.cfg
+        packed, plain = {}, {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.ln_f}
+
+        def members(t, sizes, names, prefix):
+            qw, sc, su, sv = t
+            at = 0
+            for name, rows in zip(names, sizes):
+                packed[f"{prefix}.{name}"] = (qw[at // 16:(at + rows) // 16], sc[at:at + rows], su, sv[at // 8:(at + rows) // 8])
+                at += rows
+
+        for i, L in enumerate(self.layers):
+            pre = f"model.layers.{i}"
+            members(L["qkv"], [c.q_heads * c.head_dim, c.kv_heads * c.head_dim, c.kv_heads * c.head_dim], ["q_proj", "k_proj", "v_proj"],
+                    f"{pre}.self_attn")
+            packed[f"{pre}.self_attn.o_proj"] = L["o"]
+            members(L["gate_up"], [c.intermediate, c.intermediate], ["gate_proj", "up_proj"], f"{pre}.mlp")
+            packed[f"{pre}.mlp.down_proj"] = L["down"]
+            plain[f"{pre}.input_layernorm.weight"] = L["ln1"]
+            plain[f"{pre}.post_attention_layernorm.weight"] = L["ln2"]
+        packed["lm_head"] = self.head
+        config = dict(architectures=["PackedDecoder"], num_hidden_layers=c.layers, hidden_size=c.hidden, num_attention_heads=c.q_heads,
+                      num_key_value_heads=c.kv_heads, head_dim=c.head_dim, intermediate_size=c.intermediate, vocab_size=c.vocab,
+                      rope_theta=c.rope_theta, rms_norm_eps=c.eps, max_position_embeddings=c.max_len, torch_dtype="bfloat16")
+        return checkpoint.write_checkpoint(out_dir, packed, plain, config, shards=shards)
+
+    @classmethod
+    def from_checkpoint(cls, ckpt_dir, device, fused=True, dtype=torch.bfloat16):
+        """Builds the model from a packed checkpoint through the serving plugin: `HTRConfig.from_config` picks the method per
+        module, `HTRLinearMethod.create_weights` allocates the fused parameters, and every checkpoint tensor reaches them
+        through their `weight_loader` (htr/vllm_plugin.py:40-125 of the reference)."""
+        from vllm.model_executor.layers.linear import LinearBase
+
+        from . import checkpoint, vllm_plugin
+
+        hf = checkpoint.read_config(ckpt_dir)
+        qc = vllm_plugin.HTRConfig.from_config(hf["quantization_config"])
+        qc.packed_modules_mapping = {"qkv_proj": ["q_proj", "k_proj", "v_proj"], "gate_up_proj": ["gate_proj", "up_proj"]}
+        c = DecoderConfig(layers=hf["num_hidden_layers"], hidden=hf["hidden_size"], q_heads=hf["num_attention_heads"],
+                          kv_heads=hf["num_key_value_heads"], head_dim=hf["head_dim"], intermediate=hf["intermediate_size"],
+                          vocab=hf["vocab_size"], max_len=hf.get("max_position_embeddings", 512), rope_theta=hf["rope_theta"],
+                          eps=hf["rms_norm_eps"])
+        params, holders = {}, {}
+
+        def linear(prefix, n, sizes, lm_head=False):
+            holder = LinearBase.__new__(LinearBase)            # only its type matters to get_quant_method
+            torch.nn.Module.__init__(holder)
+            method = vllm_plugin.HTRLinearMethod(qc.modules["lm_head"]) if lm_head else qc.get_quant_method(holder, prefix)
+            assert isinstance(method, vllm_plugin.HTRLinearMethod), f"{prefix} is not packed in this checkpoint"
+            method.create_weights(holder, n, sizes, n, sum(sizes), dtype)
+            for leaf in ("htr_qweight", "htr_scales", "htr_su", "htr_sv"):
+                params[f"{prefix}.{leaf}"] = getattr(holder, leaf)
+            holders[prefix] = holder
+            return holder
+
+        def plain(name, shape):
+            params[name] = torch.nn.Parameter(torch.empty(shape, dtype=dtype), requires_grad=False)
+            return params[name]
+
+        plain("model.embed_tokens.weight", (c.vocab, c.hidden))
+        plain("model.norm.weight", (c.hidden,))
+        for i in range(c.layers):
+            pre = f"model.layers.{i}"
+            linear(f"{pre}.self_attn.qkv_proj", c.hidden, [c.q_heads * c.head_dim, c.kv_heads * c.head_dim, c.kv_heads * c.head_dim])
+            linear(f"{pre}.self_attn.o_proj", c.q_heads * c.head_dim, [c.hidden])
+            linear(f"{pre}.mlp.gate_up_proj", c.hidden, [c.intermediate, c.intermediate])
+            linear(f"{pre}.mlp.down_proj", c.intermediate, [c.hidden])
+            plain(f"{pre}.input_layernorm.weight", (c.hidden,))
+            plain(f"{pre}.post_attention_layernorm.weight", (c.hidden,))
+        linear("lm_head", c.hidden, [c.vocab], lm_head=True)
+        got = checkpoint.load_checkpoint(ckpt_dir, params)
+        missing = sorted(set(params) - got)
+        assert not missing, f"checkpoint lacks {missing[:4]}"
+
+        def tensors(prefix):
+            h = holders[prefix]
+            return tuple(t.data.to(device) for t in (h.htr_qweight, h.htr_scales, h.htr_su, h.htr_sv))
+
+        K_trunk = holders["model.layers.0.self_attn.qkv_proj"].htr_K if c.layers else 4
+        c.K, c.K_head = K_trunk, holders["lm_head"].htr_K
+        layers = []
+        for i in range(c.layers):
+            pre = f"model.layers.{i}"
+            layers.append(dict(qkv=tensors(f"{pre}.self_attn.qkv_proj"), o=tensors(f"{pre}.self_attn.o_proj"),
+                               gate_up=tensors(f"{pre}.mlp.gate_up_proj"), down=tensors(f"{pre}.mlp.down_proj"),
+                               ln1=params[f"{pre}.input_layernorm.weight"].data.to(device),
+                               ln2=params[f"{pre}.post_attention_layernorm.weight"].data.to(device)))
+        weights = dict(layers=layers, head=tensors("lm_head"), ln_f=params["model.norm.weight"].data.to(device),
+                       embed=params["model.embed_tokens.weight"].data.to(device))
+        return cls(c, device, dtype=dtype, fused=fused, weights=weights)
 
     def packed_bytes_per_token(self):
         """Packed payload read by one decode step (every trunk linear once + the LM head)."""

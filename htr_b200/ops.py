@@ -93,6 +93,39 @@ def _gemv(x2, qweight, scales, su, sv, bias, out):
     _lib.check(rc, "htr_linear")
 
 
+def linear_padded(x, qweight, scales, su, sv, bias=None, m_out=None):
+    """Packed linear whose stored tensors cover a zero-padded [m_pad, n_pad] matrix: x[..., n_in] with n_in <= n_pad,
+    result [..., m_out] with m_out <= m_pad (bias, if any, has m_out elements).
+
+    The reference's `HTRHCLinearMethod.apply` (htr/vllm_plugin.py:313-326) pads the input with `F.pad` and slices the output
+    with `.contiguous()`; here both happen inside the kernel (missing columns are read as zeros, rows beyond m_out are not
+    written).  n_in and m_out must be multiples of 8.  Batches above 8 rows run as 8-row launches."""
+    mt, nt, W = qweight.shape
+    m_out = mt * 16 if m_out is None else int(m_out)
+    n_in = x.shape[-1]
+    x2 = x.reshape(-1, n_in).contiguous()
+    if not x2.is_cuda:
+        raise _lib.HTRError("htr::linear has no CPU path: tensors must live on a CUDA device")
+    if x2.dtype not in _DTYPES:
+        raise _lib.HTRError(f"htr::linear: unsupported activation dtype {x2.dtype}")
+    if bias is not None and (bias.dtype != x2.dtype or bias.numel() != m_out):
+        raise _lib.HTRError("htr::linear: bias must have the activation dtype and m_out elements")
+    M, K = x2.shape[0], W // 8
+    y = torch.empty((M, m_out), dtype=x2.dtype, device=x2.device)
+    if M:
+        qweight, scales, su, sv = qweight.contiguous(), scales.contiguous(), su.contiguous(), sv.contiguous()
+        with torch.cuda.device(x2.device):
+            st = torch.cuda.current_stream(x2.device).cuda_stream
+            for r0 in range(0, M, GEMV_MAX_M):
+                rows = min(GEMV_MAX_M, M - r0)
+                ws = workspace(x2.device, _lib.lib.htr_linear_workspace_bytes(rows, mt * 16, nt * 16, K))
+                rc = _lib.lib.htr_linear_padded(x2[r0:].data_ptr(), _DTYPES[x2.dtype], rows, n_in, qweight.data_ptr(), mt, nt, K,
+                                                scales.data_ptr(), su.data_ptr(), sv.data_ptr(), None if bias is None else bias.data_ptr(),
+                                                y[r0:].data_ptr(), m_out, ws.data_ptr(), ws.numel(), st)
+                _lib.check(rc, "htr_linear_padded")
+    return y.reshape(*x.shape[:-1], m_out)
+
+
 _GEMM_WS = {}
 
 

@@ -166,6 +166,54 @@ class HTRLinearMethod(LinearMethodBase):
         return ops.linear(x, layer.htr_qweight, layer.htr_scales, layer.htr_su, layer.htr_sv, bias)
 
 
+class HTRHCLinearMethod(HTRLinearMethod):
+    """Packed linear for projections whose dimensions are not multiples of 128 (htr/vllm_plugin.py:279-326 of the reference).
+
+    spec = {"K", "m", "n", "m_pad", "n_pad"}: the stored tensors cover the zero-padded [m_pad, n_pad] matrix; the module's own
+    input width is n and its output width m_out lies in [m, m_pad].  `apply` hands the unpadded activations to
+    `ops.linear_padded`, which pads and slices inside the kernel.  A zero-storage uint8 `weight` buffer of the logical shape
+    keeps call sites that read `.weight` for its shape working, as in the reference."""
+
+    def __init__(self, spec):
+        super().__init__(int(spec["K"]))
+        self.spec = spec
+
+    def create_weights(self, layer, input_size_per_partition, output_partition_sizes, input_size, output_size, params_dtype,
+                       **extra_weight_attrs):
+        sp, K = self.spec, self.K
+        n, m_out = input_size_per_partition, sum(output_partition_sizes)
+        assert input_size_per_partition == input_size, "HTR: tensor parallelism is not supported"
+        m_pad, n_pad = int(sp["m_pad"]), int(sp["n_pad"])
+        assert n == sp["n"] and sp["m"] <= m_out <= m_pad and n <= n_pad and m_pad % 128 == 0 and n_pad % 128 == 0, (sp, n, m_out)
+        assert n % 8 == 0 and m_out % 8 == 0, "HTR: padded linears need input and output widths that are multiples of 8"
+        shapes = {"htr_qweight": ((m_pad // 16, n_pad // 16, 8 * K), torch.int32), "htr_scales": ((m_pad,), torch.float16),
+                  "htr_su": ((n_pad // 8,), torch.uint8), "htr_sv": ((m_pad // 8,), torch.uint8)}
+
+        def whole_loader(name):
+            def load(param, loaded, shard_id=None):
+                assert shard_id is None and getattr(loaded, "shard_id", None) is None, (name, shard_id)
+                assert tuple(loaded.shape) == tuple(param.shape) and loaded.dtype == param.dtype, (name, param.shape, loaded.shape)
+                param.data.copy_(loaded)
+            return load
+
+        for name, (shape, dt) in shapes.items():
+            par = Parameter(torch.empty(shape, dtype=dt), requires_grad=False)
+            layer.register_parameter(name, par)
+            set_weight_attrs(par, {"weight_loader": whole_loader(name)})
+        layer.htr_K = K
+        layer._htr_n, layer._htr_n_pad, layer._htr_m_out, layer._htr_m_pad = n, n_pad, m_out, m_pad
+        layer.register_buffer("weight", torch.zeros(1, dtype=torch.uint8).expand(m_out, n), persistent=False)
+        layer._htr_weight_carrier = True
+
+    def apply(self, layer, x, bias=None):
+        from . import ops
+
+        if _COUNT_FILE is not None:
+            _census(layer, x)
+            _COUNTS["hc"] += 1
+        return ops.linear_padded(x, layer.htr_qweight, layer.htr_scales, layer.htr_su, layer.htr_sv, bias, m_out=layer._htr_m_out)
+
+
 # optional dispatch census (htr/vllm_plugin.py:132-150): HTR_COUNT_FILE=<path> counts calls per batch bucket and width
 _COUNT_FILE = os.environ.get("HTR_COUNT_FILE") or None
 _COUNTS = collections.Counter()

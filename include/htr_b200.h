@@ -115,6 +115,15 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
 int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
                       const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, htr_stream_t stream);
 
+/* Padded form (the reference's HTRHCLinearMethod.apply, htr/vllm_plugin.py:313-326: F.pad of the input to n_pad, slice of
+ * the output to m_out, both as separate copies there): the stored tensors cover a padded [m = 16*mt, n = 16*nt] matrix, x has
+ * only n_in <= n columns per row (row stride n_in; the missing columns count as zeros) and y receives only the first
+ * m_out <= m rows (row stride m_out; bias, if given, has m_out elements).  n_in and m_out are multiples of 8.  Same kernel,
+ * workspace and limits as htr_linear (M <= HTR_GEMV_MAX_ROWS). */
+int htr_linear_padded(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
+                      const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* workspace,
+                      size_t workspace_bytes, htr_stream_t stream);
+
 /* Tensor-core form of the packed linear for prefill-sized batches, 1 <= M <= HTR_GEMM_MAX_ROWS rows per call:
  * decoded tiles go straight into the shared-memory operand of tcgen05.mma, accumulators live in TMEM; two launches
  * (activation transform to fp16 hi/lo planes, then the GEMM with the same split reduction and epilogue as the GEMV).
