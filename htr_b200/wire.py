@@ -34,6 +34,12 @@ def cbscale():
     return _CBSCALE
 
 
+def codebook_f32():
+    """cb[s] = float32(v(s) / rms) with the division in float64 (htr/wire.py:19-24), as a numpy array of 65536 values."""
+    v = gen_values(torch.arange(S)).double()
+    return (v / v.pow(2).mean().sqrt()).float().numpy()
+
+
 def pack_signs(s):
     """+-1 vector [N] -> uint8 [N/8], LSB-first, set bit = -1 (htr/wire.py:66-69)."""
     neg = (s.reshape(-1, 8) < 0).to(torch.int32)

@@ -162,6 +162,20 @@ int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, c
                       int kv_heads, int head_dim, htr_stream_t stream);
 int htr_dec_swiglu(const void* gate_up, void* out, int rows, int intermediate, htr_stream_t stream);
 
+/* Encoder-side search: tail-biting Viterbi over the bit-shift trellis, one tile per row of x[B][T] with weights w[B][T]
+ * (float32, T <= 256; the encoder uses T = 256).  Replaces htr/reference.py:7-50 (viterbi) and the CUDA module of
+ * htr/vit_v2.py:28-73 (built there for sm_86 / sm_120 only), the callable behind the reference's encode.VITERBI hook
+ * (htr/encode.py:7,48): minimises sum_t w[t] * (x[t] - cb[s_t])^2, cb[s] = float32(v(s) / rms), over state sequences
+ * s_t = ((s_{t-1} << K) & 0xFFFF) | bits; with tailbite != 0 the sequence closes into a circle.  states[B][T] receives the
+ * 16-bit states (as int32), total[B] (may be NULL) the cost of the winning final state.  The workspace holds back-pointers:
+ * htr_viterbi_workspace_bytes(B, T, K) bytes (0 = unsupported arguments).
+ * htr_codebook_f32 writes cb[0..65535] as the search computes it (test hook). */
+size_t htr_viterbi_workspace_bytes(int B, int T, int K);
+int htr_viterbi(const float* x, const float* w, int B, int T, int K, int tailbite, int32_t* states, float* total, void* workspace,
+                size_t workspace_bytes, htr_stream_t stream);
+int htr_viterbi_last_cuda_error(void);
+int htr_codebook_f32(float* out, htr_stream_t stream);
+
 /* Launch-shape knobs of htr_linear for measurements (0 = library default): CTAs per SM of the GEMV grid. */
 void htr_set_gemv_ctas_per_sm(int ctas);
 /* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */

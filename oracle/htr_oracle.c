@@ -291,6 +291,98 @@ int htro_rht(const float *x, int M, int n, const uint8_t *su8, float *xt) {
   return 0;
 }
 
+/* ---- encoder search: htr/reference.py:7-50 (viterbi) ---------------------------------------
+ * Tail-biting Viterbi over the bit-shift trellis of one tile per batch row: minimises
+ * sum_t w[t] * (x[t] - cb[s_t])^2 subject to s_t = ((s_{t-1} << K) & 0xFFFF) | new bits.  Same float32 operation order as
+ * the reference (subtract, square, times w, plus the running minimum), first minimum wins on ties (torch.min / argmin return
+ * the first minimal index), two passes for tail-biting: the low 16-K bits of the unconstrained winner become the required
+ * high bits of the first state and low bits of the last.  states: [B][T] int32, total: [B] cost of the returned path's
+ * final state (pass-2 value).  Returns 0, or -1 on bad arguments / allocation failure. */
+int htro_viterbi(const float *x, const float *w, size_t B, int T, int K, int tailbite, int32_t *states, float *total) {
+  if (K < 1 || K > 8 || T < 1) return -1;
+  const uint32_t nb = 1u << K, Sj = HTRO_STATES >> K;
+  float *cb = (float *)malloc(HTRO_STATES * sizeof(float));
+  if (!cb) return -1;
+  htro_codebook_f32(cb);
+  int failed = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+  for (long long b = 0; b < (long long)B; ++b) {
+    float *cost = (float *)malloc(HTRO_STATES * sizeof(float));
+    float *mins = (float *)malloc(Sj * sizeof(float));
+    uint8_t *bps = (uint8_t *)malloc((size_t)(T > 1 ? T - 1 : 1) * Sj);
+    if (!cost || !mins || !bps) {
+      failed = 1;
+      free(cost); free(mins); free(bps);
+      continue;
+    }
+    const float *xb = x + (size_t)b * T, *wb = w + (size_t)b * T;
+    long long j0 = -1;
+    for (int pass = 0; pass < (tailbite ? 2 : 1); ++pass) {
+      for (uint32_t s = 0; s < HTRO_STATES; ++s) {           /* reference.py:22-27 */
+        const float d = xb[0] - cb[s];
+        const float dd = d * d;
+        const float c = wb[0] * dd;
+        cost[s] = (j0 >= 0 && (long long)(s >> K) != j0) ? INFINITY : c;
+      }
+      for (int t = 1; t < T; ++t) {                          /* reference.py:29-33 */
+        for (uint32_t j = 0; j < Sj; ++j) {
+          float m = cost[j];
+          uint32_t arg = 0;
+          for (uint32_t top = 1; top < nb; ++top) {
+            const float v = cost[top * Sj + j];
+            if (v < m) { m = v; arg = top; }
+          }
+          mins[j] = m;
+          bps[(size_t)(t - 1) * Sj + j] = (uint8_t)arg;
+        }
+        for (uint32_t j = 0; j < Sj; ++j)
+          for (uint32_t a = 0; a < nb; ++a) {
+            const float d = xb[t] - cb[j * nb + a];
+            const float dd = d * d;
+            const float wd = wb[t] * dd;
+            cost[j * nb + a] = mins[j] + wd;
+          }
+      }
+      if (tailbite && pass == 0) {                           /* reference.py:36-38 */
+        uint32_t best = 0;
+        for (uint32_t s = 1; s < HTRO_STATES; ++s)
+          if (cost[s] < cost[best]) best = s;
+        j0 = best & (Sj - 1);
+      }
+    }
+    uint32_t s = 0;                                          /* reference.py:39-42 */
+    int have = 0;
+    for (uint32_t c = 0; c < HTRO_STATES; ++c) {
+      if (tailbite && (long long)(c & (Sj - 1)) != j0) continue;
+      if (!have || cost[c] < cost[s]) { s = c; have = 1; }
+    }
+    if (total) total[b] = cost[s];
+    states[(size_t)b * T + T - 1] = (int32_t)s;
+    for (int t = T - 1; t >= 1; --t) {                       /* reference.py:45-49 */
+      const uint32_t low = s >> K;
+      s = (uint32_t)bps[(size_t)(t - 1) * Sj + low] * Sj + low;
+      states[(size_t)b * T + t - 1] = (int32_t)s;
+    }
+    free(cost); free(mins); free(bps);
+  }
+  free(cb);
+  return failed ? -1 : 0;
+}
+
+/* cost of a given path under the same arithmetic, summed in double (independent check of a search result) */
+double htro_path_cost(const float *x, const float *w, int T, const int32_t *states) {
+  float *cb = (float *)malloc(HTRO_STATES * sizeof(float));
+  if (!cb) return -1.0;
+  htro_codebook_f32(cb);
+  double acc = 0.0;
+  for (int t = 0; t < T; ++t) {
+    const double d = (double)x[t] - (double)cb[states[t] & 0xFFFF];
+    acc += (double)w[t] * d * d;
+  }
+  free(cb);
+  return acc;
+}
+
 int htro_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -151,7 +151,7 @@ def build(force=False):
     src = os.path.join(HERE, "htr_oracle.c")
     if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= os.path.getmtime(src):
         return LIB_PATH
-    subprocess.run(["gcc", "-O3", "-march=x86-64-v2", "-fopenmp", "-fPIC", "-shared", "-o", LIB_PATH, src, "-lm"], check=True)
+    subprocess.run(["gcc", "-O3", "-march=x86-64-v2", "-ffp-contract=off", "-fopenmp", "-fPIC", "-shared", "-o", LIB_PATH, src, "-lm"], check=True)
     return LIB_PATH
 
 
@@ -254,6 +254,29 @@ class COracle:
                                   None if b is None else _p(b, ctypes.c_float), mt, nt, W // 8, _p(out, ctypes.c_float))
         assert rc == 0
         return out
+
+    def viterbi(self, x, w, K, tailbite=True, threads=None):
+        """Tail-biting trellis search per row of x [B, T] with weights w (htr/reference.py:7-50).  Returns (states int32 [B, T],
+        float32 [B] cost of the winning final state)."""
+        if threads:
+            self.lib.htro_set_num_threads(int(threads))
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        B, T = x.shape
+        states = np.empty((B, T), dtype=np.int32)
+        total = np.empty(B, dtype=np.float32)
+        rc = self.lib.htro_viterbi(_p(x, ctypes.c_float), _p(w, ctypes.c_float), ctypes.c_size_t(B), T, int(K), int(bool(tailbite)),
+                                   _p(states, ctypes.c_int32), _p(total, ctypes.c_float))
+        assert rc == 0
+        return states, total
+
+    def path_cost(self, x, w, states):
+        """Cost of a path under the same error measure, accumulated in float64."""
+        self.lib.htro_path_cost.restype = ctypes.c_double
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w = np.ascontiguousarray(w, dtype=np.float32)
+        st = np.ascontiguousarray(states, dtype=np.int32)
+        return float(self.lib.htro_path_cost(_p(x, ctypes.c_float), _p(w, ctypes.c_float), x.shape[-1], _p(st, ctypes.c_int32)))
 
     def num_threads(self):
         return int(self.lib.htro_num_threads())

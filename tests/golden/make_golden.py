@@ -17,6 +17,9 @@ repository's code.  Fixtures:
   encoded_K4.npz    encoder round trip of tests/test_release.py:53-73 (seed 12, 128x128, H = I)
   encoded_hessian_K{2,3}.npz  small Hessian-weighted encodes (the outlier-channel recipe of the
                     benchmark configs, shrunk to 128x256)
+  viterbi.npz       htr/reference.py viterbi (the encoder's trellis search) on seeded tiles: targets, weights, the states it
+                    returns and their cost, K2..K5 tail-biting + K4 without tail-biting + K6/K8 on one tile
+                    (only with --viterbi, it takes a few minutes)
 """
 import argparse
 import hashlib
@@ -33,12 +36,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the HTR checkout")
     ap.add_argument("--out", default=HERE)
+    ap.add_argument("--viterbi", action="store_true", help="write viterbi.npz only")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from htr import encode, wire
 
     torch.set_num_threads(os.cpu_count())
     out = a.out
+    if a.viterbi:
+        return viterbi_fixture(out)
 
     # ---- codebook
     v = wire.gen_values(torch.arange(65536))
@@ -116,6 +122,30 @@ def main():
     finally:
         encode.VITERBI = old
     print("wrote fixtures to", out)
+
+
+def viterbi_fixture(out):
+    """Inputs shaped like the encoder's calls (htr/encode.py:77-86): targets = rows of a rotated weight divided by the row
+    scale (about unit variance in codebook units), weights = squared row scales normalised to mean 1 per tile."""
+    from htr import reference, wire
+
+    cb = wire.codebook_f32()
+    d = {}
+    cases = [(2, 3, True), (3, 3, True), (4, 3, True), (5, 3, True), (4, 2, False), (6, 1, True), (8, 1, True)]
+    for K, B, tb in cases:
+        g = torch.Generator().manual_seed(100 * K + int(tb))
+        x = torch.randn(B, 256, generator=g) * (1.0 + 0.25 * torch.rand(B, 1, generator=g))
+        x[0, :5] *= 4.0                                             # a few outliers beyond the codebook range
+        rs = (torch.rand(B, 16, generator=g) + 0.5).repeat_interleave(16, dim=1) ** 2
+        w = rs / rs.mean(dim=1, keepdim=True)
+        st = reference.viterbi(x, w, cb, K, tailbite=tb)
+        cost = (w * (x - cb[st]) ** 2).sum(dim=1)
+        tag = f"K{K}" + ("" if tb else "_open")
+        d[tag + "_x"], d[tag + "_w"] = x.numpy(), w.numpy()
+        d[tag + "_states"], d[tag + "_cost"] = st.numpy().astype(np.int32), cost.numpy()
+        print(tag, "cost", cost.tolist())
+    np.savez_compressed(os.path.join(out, "viterbi.npz"), **d)
+    print("wrote", os.path.join(out, "viterbi.npz"))
 
 
 if __name__ == "__main__":

@@ -98,3 +98,23 @@ def test_real_encoder_streams_decode_to_the_encoder_output(golden, coracle, name
 def test_payload_accounting():
     # docs/EVIDENCE.md:36-41 of the reference
     assert [O.payload_bytes(4096, 4096, K) for K in WIDTHS] == [4203520, 6300672, 8397824, 10494976]
+
+
+VITERBI_CASES = (("K2", 2, True), ("K3", 3, True), ("K4", 4, True), ("K5", 5, True), ("K4_open", 4, False), ("K6", 6, True), ("K8", 8, True))
+
+
+@pytest.mark.parametrize("tag,K,tailbite", VITERBI_CASES)
+def test_trellis_search_reproduces_the_reference_search(golden, coracle, tag, K, tailbite):
+    """htr/reference.py:7-50 run on seeded tiles when the fixture was made: same states, same cost."""
+    g = golden("viterbi")
+    x, w, want = g[tag + "_x"], g[tag + "_w"], g[tag + "_states"]
+    states, total = coracle.viterbi(x, w, K, tailbite=tailbite)
+    assert np.array_equal(states, want)
+    # the trellis constraint and, with tail-biting, the circular closure (rate exactly K bits per weight)
+    mask = 0xFFFF
+    assert np.array_equal(states[:, 1:] >> K, states[:, :-1] & (mask >> K))
+    if tailbite:
+        assert np.array_equal(states[:, 0] >> K, states[:, -1] & (mask >> K))
+    for b in range(x.shape[0]):
+        assert abs(coracle.path_cost(x[b], w[b], states[b]) - float(g[tag + "_cost"][b])) <= 1e-4 * float(g[tag + "_cost"][b])
+        assert abs(float(total[b]) - float(g[tag + "_cost"][b])) <= 1e-4 * float(g[tag + "_cost"][b])
