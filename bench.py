@@ -375,6 +375,7 @@ def run_extra(args):
     lmhead   151936x4096 K4 LM head, batch 1 and 8, rows sharded over the ranks (strong scaling), peer-store gather
     decoder  the 9B-class dense decoder, K4 trunk + K4 head, 16-token prompt + 256 greedy tokens, one sequence
     moe      64 experts, top-8, SwiGLU 4096->1536->4096, K3, 1..32 tokens per step
+    viterbi  the encoder's trellis search: 1024 tiles per call (the reference encoder's batch), K2..K5, with a CPU sample
     Prints one JSON line per workload (rank 0)."""
     import torch
     import torch.distributed as dist
@@ -466,6 +467,32 @@ def run_extra(args):
                 print(json.dumps({"metric": "moe_layer_ms", "unit": "ms", "value": ms, "higher_is_better": False, "n_gpus": world,
                                   "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "packed_GBps_per_gpu": nbytes / (ms * 1e-3) / 1e9,
                                   "config": {"workload": "moe_64x_top8_swiglu_4096_1536_K3", "tokens": T, "routing": "on device; two grouped GEMV launches per layer (gate_up, down), CUDA graph"}}), flush=True)
+    elif args.workload == "viterbi":
+        from htr_b200 import encoder
+        B = 1024                                                 # max_batch of the reference encoder (htr/encode.py:47)
+        g = torch.Generator().manual_seed(5)
+        x = (torch.randn(B, 256, generator=g) * (1.0 + 0.25 * torch.rand(B, 1, generator=g))).to(dev)
+        rs = (torch.rand(B, 16, generator=g) + 0.5).repeat_interleave(16, dim=1) ** 2
+        w = (rs / rs.mean(dim=1, keepdim=True)).to(dev)
+        cpu = None
+        if not args.no_cpu:
+            sys.path.insert(0, ROOT)
+            from oracle import oracle
+            oracle.build()
+            cpu = oracle.COracle()
+        for K in (2, 3, 4, 5):
+            encoder.viterbi(x, w, None, K)
+            ms = time_graph(lambda: encoder.viterbi(x, w, None, K), max(3, args.steps // 4))
+            line = {"metric": "viterbi_tiles_per_s", "unit": "tiles/s", "value": B / (ms * 1e-3), "n_gpus": 1, "ms_per_call": ms,
+                    "us_per_tile": ms * 1e3 / B, "candidates_per_s": B * 2 * 256 * 65536 / (ms * 1e-3),
+                    "config": {"workload": "trellis_search_1024_tiles_x256_tailbiting", "K": K, "data": "synthetic N(0,1) targets, row-scale weights"}}
+            if cpu is not None:
+                nt = cpu.num_threads()
+                t0 = time.perf_counter()
+                cpu.viterbi(x[:nt].cpu().numpy(), w[:nt].cpu().numpy(), K)
+                dt = time.perf_counter() - t0
+                line["cpu_baseline"] = {"value": nt / dt, "unit": "tiles/s", "cores": nt, "kind": "port", "sample": f"{nt} tiles, one per core"}
+            print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -475,6 +502,17 @@ def run_case(spec):
     allows), each called once per repetition through `ops.linear`, eagerly.  spec: K=4,m=4096,n=12288,M=64[,copies=6,reps=1,dtype=bf16]"""
     import torch
     from htr_b200 import ops, wire
+    if spec.startswith("viterbi:"):                          # viterbi:K=4,B=592 -- one call of the trellis search on B seeded tiles
+        from htr_b200 import encoder
+        kv = dict(item.split("=") for item in spec[len("viterbi:"):].split(","))
+        K, B = int(kv["K"]), int(kv["B"])
+        g = torch.Generator().manual_seed(5)
+        x = torch.randn(B, 256, generator=g).cuda()
+        w = (torch.rand(B, 256, generator=g) + 0.5).cuda()
+        st, cost = encoder.viterbi(x, w, None, K, return_cost=True)
+        torch.cuda.synchronize()
+        print(json.dumps({"case": spec, "mean_cost": float(cost.mean())}))
+        return
     kv = dict(item.split("=") for item in spec.split(","))
     K, m, n, M = int(kv["K"]), int(kv["m"]), int(kv["n"]), int(kv["M"])
     copies, reps = int(kv.get("copies", 6)), int(kv.get("reps", 1))
@@ -497,7 +535,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
-    ap.add_argument("--workload", default="mlp", choices=("mlp", "lmhead", "decoder", "moe"),
+    ap.add_argument("--workload", default="mlp", choices=("mlp", "lmhead", "decoder", "moe", "viterbi"),
                     help="mlp = the default benchmark line; the others print lines for the remaining configurations")
     ap.add_argument("--case", default=None, help="run one small fixed case for a profiler and exit, e.g. K=4,m=4096,n=12288,M=64")
     args = ap.parse_args()

@@ -40,7 +40,10 @@ struct VitParams {
 template <int K>
 struct VitCfg {
   static constexpr int kSj = 1 << (16 - K);
-  static constexpr int kThreads = K == 2 ? 1024 : (kSj < 512 ? kSj : 512);
+  // a thread owns groups of kJb consecutive j (they share the predecessor minima: kJb divides 2^K) and works on them in pairs
+  static constexpr int kJb = K == 2 ? 4 : K <= 4 ? 8 : K == 5 ? 4 : 2;
+  static constexpr int kThreads = K == 2 ? 1024 : (kSj / kJb < 512 ? kSj / kJb : 512);
+  static constexpr int kGroups = kSj / (kThreads * kJb);
   static constexpr int kSmem = 2 * kSj * 4 + 2 * kVitMaxT * 4 + kSj;   // two cost arrays, targets, weights, last back-pointers
 };
 
@@ -48,6 +51,17 @@ __device__ __forceinline__ float codebook_value(uint32_t hash, float inv_hi, flo
   const float v = __uint_as_float(__dp4a(hash, 0x01010101u, kMagicBits - 510u)) - 12582912.0f;   // the integer v(s), exactly
   return __fmaf_rn(v, inv_hi, __fmul_rn(v, inv_lo));
 }
+
+// packed float32 pairs (one instruction, two candidates); HTR_VIT_SCALAR builds the same arithmetic from scalar instructions
+#ifdef HTR_VIT_SCALAR
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y)); }
+#else
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+#endif
 
 struct Best {
   float v;
@@ -57,7 +71,8 @@ __device__ __forceinline__ bool better(const Best& a, const Best& b) { return a.
 
 template <int K>
 __global__ void __launch_bounds__(VitCfg<K>::kThreads) viterbi_kernel(const VitParams p) {
-  constexpr int NB = 1 << K, SJ = VitCfg<K>::kSj, SH = 16 - 2 * K, THREADS = VitCfg<K>::kThreads;
+  constexpr int NB = 1 << K, SJ = VitCfg<K>::kSj, SH = 16 - 2 * K, THREADS = VitCfg<K>::kThreads, JB = VitCfg<K>::kJb, GROUPS = VitCfg<K>::kGroups;
+  static_assert(JB >= 2 && JB % 2 == 0 && NB % JB == 0 && GROUPS * THREADS * JB == SJ, "thread-to-state mapping");
   constexpr uint32_t kTopStep = kGenMul << (16 - K);                      // hash difference between consecutive top values
   extern __shared__ __align__(16) unsigned char vsm[];
   float* m_a = reinterpret_cast<float*>(vsm);
@@ -70,6 +85,8 @@ __global__ void __launch_bounds__(VitCfg<K>::kThreads) viterbi_kernel(const VitP
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int T = p.T;
   uint8_t* bp = p.bps + (size_t)blockIdx.x * T * SJ;
+  const float2 unmagic = make_float2(-12582912.0f, -12582912.0f);
+  const float2 ninv_hi = make_float2(-p.inv_hi, -p.inv_hi), ninv_lo = make_float2(-p.inv_lo, -p.inv_lo);
 
   for (int tile = blockIdx.x; tile < p.B; tile += gridDim.x) {
     __syncthreads();                                                     // the previous tile's traceback is over
@@ -86,27 +103,64 @@ __global__ void __launch_bounds__(VitCfg<K>::kThreads) viterbi_kernel(const VitP
       for (int j = tid; j < SJ; j += THREADS) mc[j] = (j0 < 0 || j == j0) ? 0.f : INFINITY;
       __syncthreads();
       for (int t = 0; t < T; ++t) {
-        const float xt = xs[t], wt = ws[t];
+        const float2 xt2 = make_float2(xs[t], xs[t]), wt2 = make_float2(ws[t], ws[t]);
         const bool last = t == T - 1;
-        for (int j = tid; j < SJ; j += THREADS) {
-          const uint32_t hbase = (uint32_t)j * kGenMul + kGenAdd;
-          const int u = j >> K;
-          float best = INFINITY;
-          int arg = 0;
-#pragma unroll 8
+#pragma unroll 1
+        for (int g = 0; g < GROUPS; ++g) {
+          const int jbase = (g * THREADS + tid) * JB;
+          const float* prev_col = mc + (jbase >> K);                     // predecessor minima of this group: stride 2^(16-2K) per top
+          uint32_t hash[JB];
+          float best[JB];
+          int arg[JB];
+#pragma unroll
+          for (int b = 0; b < JB; ++b) {
+            hash[b] = (uint32_t)(jbase + b) * kGenMul + kGenAdd;
+            best[b] = INFINITY;
+            arg[b] = 0;
+          }
+#pragma unroll 4
           for (int top = 0; top < NB; ++top) {
-            const float prev = mc[(top << SH) | u];
-            const float c = codebook_value(hbase + (uint32_t)top * kTopStep, p.inv_hi, p.inv_lo);
-            const float d = __fsub_rn(xt, c);
-            const float v = __fadd_rn(prev, __fmul_rn(wt, __fmul_rn(d, d)));   // the reference's order: square, times w, plus the minimum
-            if (v < best) {                                              // strict: the first minimum wins, as torch.min does
-              best = v;
-              arg = top;
+            const float prev = prev_col[top << SH];
+#pragma unroll
+            for (int b = 0; b < JB; b += 2) {
+              // two candidates per packed float instruction; per lane the reference's operation order:
+              // c = float32(v / rms); d = x - c; cost = prev + w * (d * d)
+              const float2 vm = make_float2(__uint_as_float(bytesum_add_alu(hash[b], kMagicBits - 510u)),
+                                            __uint_as_float(bytesum_add(hash[b + 1], kMagicBits - 510u)));
+              const float2 v = add2(vm, unmagic);
+              const float2 negc = fma2(v, ninv_hi, mul2(v, ninv_lo));              // -c: negation commutes with rounding
+              const float2 d = add2(xt2, negc);
+              const float2 wd = mul2(wt2, mul2(d, d));
+              // the last addition stays scalar: a packed multiply followed by a packed add was observed to come out fused (one
+              // rounding instead of two, costs 1 ulp off the reference's), which separate scalar adds rule out
+              const float2 val = make_float2(__fadd_rn(prev, wd.x), __fadd_rn(prev, wd.y));
+              if (val.x < best[b]) { best[b] = val.x; arg[b] = top; }              // strict: the first minimum wins, as torch.min does
+              if (val.y < best[b + 1]) { best[b + 1] = val.y; arg[b + 1] = top; }
+              hash[b] += kTopStep;
+              hash[b + 1] += kTopStep;
             }
           }
-          mn[j] = best;
-          if (keep) bp[(size_t)t * SJ + j] = (uint8_t)arg;
-          if (last) lastarg[j] = (uint8_t)arg;
+          uint32_t packed_arg[(JB + 3) / 4];
+#pragma unroll
+          for (int q = 0; q < (JB + 3) / 4; ++q) packed_arg[q] = 0u;
+#pragma unroll
+          for (int b = 0; b < JB; ++b) {
+            mn[jbase + b] = best[b];
+            packed_arg[b >> 2] |= (uint32_t)arg[b] << (8 * (b & 3));
+          }
+          if constexpr (JB >= 4) {
+            if (keep) {
+#pragma unroll
+              for (int q = 0; q < JB / 4; ++q) *reinterpret_cast<uint32_t*>(bp + (size_t)t * SJ + jbase + 4 * q) = packed_arg[q];
+            }
+            if (last) {
+#pragma unroll
+              for (int q = 0; q < JB / 4; ++q) *reinterpret_cast<uint32_t*>(lastarg + jbase + 4 * q) = packed_arg[q];
+            }
+          } else {
+            if (keep) *reinterpret_cast<uint16_t*>(bp + (size_t)t * SJ + jbase) = (uint16_t)packed_arg[0];
+            if (last) *reinterpret_cast<uint16_t*>(lastarg + jbase) = (uint16_t)packed_arg[0];
+          }
         }
         __syncthreads();
         float* sw = mc; mc = mn; mn = sw;
