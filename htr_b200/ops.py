@@ -5,10 +5,11 @@ method, or any torch code) switches by importing this module instead.  The dispa
 for one B200 (148 SMs, HBM3e) rather than copied from the 40-CU part the reference was tuned on:
 
   M == 0            empty result                                             (htr/ops.py:73-74)
-  1 <= M <= 8       one launch of the streaming GEMV (activation transform, decode + dot, split reduce,
+  1 <= M <= 4       one launch of the streaming GEMV (activation transform, decode + dot, split reduce,
                     output transform fused)                                  (replaces htr/ops.py:75-76,95-101)
-  8 < M <= 512      the tensor-core packed GEMM (tcgen05 + TMEM), up to 256 rows per launch (128 for float32
-                    activations); decoded tiles go straight into the MMA operand    (replaces htr/ops.py:77-93)
+  4 < M <= 512      the tensor-core packed GEMM (tcgen05 + TMEM), up to 256 rows per launch (128 for float32
+                    activations); decoded tiles go straight into the MMA operand    (replaces htr/ops.py:77-93).
+                    The GEMV handles up to 8 rows and HTR_GEMV_ROUTE_MAX=8 keeps them there; measured, the GEMM wins from 5.
   M > 512           original-basis bf16 weight from the dequant kernel (decoded once), then a library GEMM
                                                                              (htr/ops.py:89-93)
   HTR_GEMM=0        instead: GEMV over 8-row chunks up to HTR_GEMV_LOOP_MAX rows, beyond that the original-basis bf16
@@ -30,6 +31,9 @@ USE_GEMM = os.environ.get("HTR_GEMM", "1") == "1"
 GEMM_MAX_M = _lib.GEMM_MAX_ROWS
 # above this many rows the weight is decoded once to bf16 and a library GEMM runs (the packed GEMM decodes once per 256-row launch)
 GEMM_ROUTE_MAX = int(os.environ.get("HTR_GEMM_ROUTE_MAX", "512"))
+# batches above this many rows leave the GEMV for the tensor-core GEMM (the GEMV itself handles up to 8 rows, but from 5 rows
+# on the GEMM is faster: 25 us against 41-44 us at 4096x12288, 190 us against 384-408 us on the 151936x4096 head)
+GEMV_ROUTE_MAX = min(GEMV_MAX_M, int(os.environ.get("HTR_GEMV_ROUTE_MAX", "4")))
 
 _FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
 
@@ -218,7 +222,7 @@ def _linear_impl(x2, qweight, scales, su, sv, bias):
     qweight, scales, su, sv = qweight.contiguous(), scales.contiguous(), su.contiguous(), sv.contiguous()
     bias = None if bias is None else bias.contiguous()
     with torch.cuda.device(x2.device):
-        if GEMV_MAX_M < M <= GEMM_ROUTE_MAX and USE_GEMM:
+        if GEMV_ROUTE_MAX < M <= GEMM_ROUTE_MAX and USE_GEMM:
             y = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
             step = _lib.GEMM_MAX_ROWS_F32 if x2.dtype == torch.float32 else GEMM_MAX_M
             for r0 in range(0, M, step):

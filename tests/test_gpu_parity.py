@@ -22,6 +22,15 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True)
+def gemv_up_to_eight_rows(monkeypatch):
+    """This file is about the streaming GEMV: keep batches of 5..8 rows on it (by default they take the tensor-core GEMM,
+    which tests/test_gpu_gemm.py covers)."""
+    from htr_b200 import ops
+
+    monkeypatch.setattr(ops, "GEMV_ROUTE_MAX", 8)
+
+
 def rel(a, b):
     return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / max(np.linalg.norm(b.astype(np.float64)), 1e-30))
 
