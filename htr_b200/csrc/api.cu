@@ -128,7 +128,8 @@ extern "C" {
 
 static int launch_linear(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
                          const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
-                         int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags);
+                         int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags,
+                         int prologue = 0, const void* norm_w = nullptr, float eps = 0.f, int residual = 0);
 
 
 const char* htr_status_string(int status) {
@@ -218,10 +219,21 @@ int htr_linear_padded(const void* x, int dtype, int M, int n_in, const void* qwe
                        stream, 0u);
 }
 
+int htr_linear_fused(const void* x, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                     const uint8_t* sv, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream, int prologue,
+                     const void* norm_weight, float eps, int residual) {
+  if (prologue < HTR_PROLOGUE_NONE || prologue > HTR_PROLOGUE_SWIGLU || (residual != 0 && residual != 1)) return HTR_ERR_BAD_SHAPE;
+  if (prologue == HTR_PROLOGUE_RMSNORM && (!norm_weight || !aligned16(norm_weight))) return norm_weight ? HTR_ERR_ALIGNMENT : HTR_ERR_NULL;
+  if (mt <= 0 || nt <= 0) return HTR_ERR_BAD_SHAPE;
+  return launch_linear(x, HTR_DTYPE_BF16, M, nt * 16, qweight, mt, nt, K, scales, su, sv, nullptr, y, mt * 16, nullptr, 0, 0, workspace,
+                       workspace_bytes, stream, 0u, prologue, norm_weight, eps, residual);
+}
+
 // shared body of the single-problem entry points: x has n_in <= n columns (the rest read as zeros), y gets the first m_out <= m rows
 static int launch_linear(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
                          const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
-                         int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags) {
+                         int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags, int prologue,
+                         const void* norm_w, float eps, int residual) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (M < 0 || M > HTR_GEMV_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
@@ -261,6 +273,11 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
   p.n_in = n_in;
   p.m_out = m_out;
+  p.prologue = prologue;
+  p.residual = residual;
+  p.x_stride = prologue == 2 ? 2 * n_in : n_in;
+  p.norm_w = norm_w;
+  p.eps = eps;
   p.group = 0;
   p.rb_per_problem = 0;
   p.g_x = nullptr; p.g_qw = nullptr; p.g_scales = nullptr; p.g_su = nullptr; p.g_sv = nullptr; p.g_y = nullptr;
@@ -333,6 +350,11 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
   p.npeer = 0;
   p.n_in = nt * 16;
   p.m_out = mt * 16;
+  p.prologue = 0;
+  p.residual = 0;
+  p.x_stride = nt * 16;
+  p.norm_w = nullptr;
+  p.eps = 0.f;
   p.peer_offset = 0;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
   p.group = count;

@@ -76,6 +76,12 @@ struct GemvParams {
   int independent;  // 1: x, bias and y are untouched by the preceding kernel of the stream (wait only before publishing)
   int n_in;         // columns present in x (row stride of x); columns n_in .. n-1 of the stored weight see zeros
   int m_out;        // rows written to y (row stride of y, length of bias); rows m_out .. m-1 of the stored weight are dropped
+  // Decoder fusions (bf16 only; the roundings of the unfused bf16 operators are reproduced):
+  int prologue;     // 0: x as given; 1: x <- rmsnorm(x) * norm_w (row-wise, eps); 2: x holds [gate | up] rows of 2n, x <- silu(gate) * up
+  int residual;     // 1: y <- y + result (y is the residual stream, read and written in place)
+  int x_stride;     // elements between activation rows (n_in; 2n for prologue 2)
+  const void* norm_w;
+  float eps;
   float cb;
   // Peer form (row-sharded linears over NVLink): when npeer > 0 the epilogue writes its rows into every listed buffer
   // (peers' and its own, plain stores through peer-mapped addresses) at element offset peer_offset, instead of into y.
@@ -97,6 +103,25 @@ struct GemvParams {
 // four consecutive activations of row r at column col (a multiple of 4); columns at or beyond n_in (a multiple of 4) read as zero
 __device__ __forceinline__ float4 load_x(const void* x, int r, int col, int n_in, int dtype) {
   return col < n_in ? load_quad(x, (size_t)r * n_in + col, dtype) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// the activation a decoder layer would have materialised in bf16 before this linear, recomputed from its inputs
+__device__ __forceinline__ float4 fused_x(const GemvParams& p, const void* x, int r, int col, float inv) {
+  if (p.prologue == 1) {                                  // RMSNorm: normalise, round, scale, round (the order of the unfused operators)
+    const float4 v = load_quad(x, (size_t)r * p.x_stride + col, p.dtype);
+    const float4 g = load_quad(p.norm_w, col, p.dtype);
+    return make_float4(bf16_round(bf16_round(v.x * inv) * g.x), bf16_round(bf16_round(v.y * inv) * g.y),
+                       bf16_round(bf16_round(v.z * inv) * g.z), bf16_round(bf16_round(v.w * inv) * g.w));
+  }
+  if (p.prologue == 2) {                                  // SwiGLU: silu(gate) rounded, times up, rounded
+    const float4 g = load_quad(x, (size_t)r * p.x_stride + col, p.dtype);
+    const float4 u = load_quad(x, (size_t)r * p.x_stride + (p.x_stride >> 1) + col, p.dtype);
+    return make_float4(bf16_round(bf16_round(g.x / (1.f + __expf(-g.x))) * u.x), bf16_round(bf16_round(g.y / (1.f + __expf(-g.y))) * u.y),
+                       bf16_round(bf16_round(g.z / (1.f + __expf(-g.z))) * u.z), bf16_round(bf16_round(g.w / (1.f + __expf(-g.w))) * u.w));
+  }
+  return load_x(x, r, col, p.n_in, p.dtype);
 }
 
 // owner CTA of unit x when CTA b starts at floor(b*U/G)
@@ -286,6 +311,34 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     predecessor_done = true;
   }
   bool ring_primed = false;                        // stages 1.. are issued behind the first activation loads
+  __shared__ float s_row_inv[MT];                  // RMSNorm scale per activation row (prologue 1)
+  if (p.prologue == 1) {
+    // RMSNorm fused into the activation staging: every CTA finds the row scale itself (the row is a few KB in L2), with the
+    // copy ring fully primed first so that the weights keep streaming meanwhile
+#pragma unroll
+    for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
+    ring_primed = true;
+    __shared__ float s_ss[kGemvWarps];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+      if (r < p.rows) {
+        float ss = 0.f;
+        for (int e = tid; e < (n >> 2); e += kGemvThreads) {
+          const float4 v = load_quad(x_ptr, (size_t)r * p.x_stride + 4 * e, p.dtype);
+          ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(kFullWarp, ss, o);
+        __syncthreads();
+        if (lane == 0) s_ss[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < kGemvWarps; ++k) tot += s_ss[k];
+        if (tid == 0) s_row_inv[r] = rsqrtf(tot / (float)n + p.eps);   // read after the barrier that opens the first staging
+      }
+    }
+  }
 
   float2 acc[MT][2];
 #pragma unroll
@@ -303,7 +356,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     const int items = MT * (hb1 - hb0);
     float4 xv_first = make_float4(0.f, 0.f, 0.f, 0.f);
     if (warp < items && warp / (hb1 - hb0) < p.rows)                // the first item's loads go out before the copy burst
-      xv_first = load_x(x_ptr, warp / (hb1 - hb0), (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.n_in, p.dtype);
+      xv_first = fused_x(p, x_ptr, warp / (hb1 - hb0), (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[warp / (hb1 - hb0)] : 1.f);
     if (!ring_primed) {
 #pragma unroll
       for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
@@ -313,7 +366,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       const int r = item / (hb1 - hb0), hb = hb0 + item % (hb1 - hb0);
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (r < p.rows) {
-        const float4 xv = item == warp ? xv_first : load_x(x_ptr, r, hb * 128 + 4 * lane, p.n_in, p.dtype);
+        const float4 xv = item == warp ? xv_first : fused_x(p, x_ptr, r, hb * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[r] : 1.f);
         const unsigned sg = sign_nibble(su_ptr, hb * 32 + lane);
         v[0] = flip(xv.x, sg & 1u); v[1] = flip(xv.y, (sg >> 1) & 1u); v[2] = flip(xv.z, (sg >> 2) & 1u); v[3] = flip(xv.w, sg >> 3);
         wht128(v, lane);
@@ -427,6 +480,10 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
                              flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
       o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
       if (p.npeer == 0) {
+        if (p.residual) {                              // y is the residual stream: add the (bf16-rounded) result in place
+          const float4 old = load_quad(y_ptr, (size_t)r * p.m_out + row0, p.dtype);
+          o = make_float4(old.x + bf16_round(o.x), old.y + bf16_round(o.y), old.z + bf16_round(o.z), old.w + bf16_round(o.w));
+        }
         if (row0 < p.m_out) store_quad(y_ptr, (size_t)r * p.m_out + row0, p.dtype, o);
       } else {
 #pragma unroll 1

@@ -46,6 +46,7 @@ class PackedDecoder:
         """Random packed weights from `seed`, or `weights` = dict(layers=[{qkv, o, gate_up, down, ln1, ln2}], head, ln_f, embed)
         already on `device` (see from_checkpoint)."""
         self.cfg, self.device, self.dtype, self.fused = cfg, device, dtype, fused
+        self.fold = True                                       # decode-sized steps: fold norms / SwiGLU / residual adds into the GEMVs
         assert cfg.max_len <= 1024, "the attention glue kernel holds at most 1024 positions"
         c = cfg
         if weights is None:
@@ -190,6 +191,8 @@ class PackedDecoder:
         """The same step with the library's glue kernels (bf16 only)."""
         c, L_ = self.cfg, _lib.lib
         T = ids.shape[0]
+        if T <= ops.GEMV_MAX_M and self.fold:
+            return self.forward_folded(ids, pos)
         dev = self.device
         st = torch.cuda.current_stream(dev).cuda_stream
         x = self.embed.index_select(0, ids)                     # residual stream, updated in place
@@ -216,6 +219,28 @@ class PackedDecoder:
         _lib.check(L_.htr_dec_add_rmsnorm(x.data_ptr(), delta.data_ptr(), self.ln_f.data_ptr(), h.data_ptr(), T, c.hidden, c.eps, st),
                    "htr_dec_add_rmsnorm")
         return ops.linear(h, *self.head)
+
+    def forward_folded(self, ids, pos):
+        """Decode-sized step (at most 8 rows) with the norms, the SwiGLU and the residual adds folded into the packed GEMVs
+        (`ops.linear_fused`): six launches per layer instead of nine."""
+        c, L_ = self.cfg, _lib.lib
+        T = ids.shape[0]
+        dev = self.device
+        st = torch.cuda.current_stream(dev).cuda_stream
+        x = self.embed.index_select(0, ids)                     # residual stream, updated in place by the o and down projections
+        q = torch.empty(T, c.q_heads, c.head_dim, dtype=self.dtype, device=dev)
+        att = torch.empty_like(q)
+        for li, L in enumerate(self.layers):
+            qkv = ops.linear_fused(x, *L["qkv"], prologue=ops.PROLOGUE_RMSNORM, norm_weight=L["ln1"], eps=c.eps)
+            _lib.check(L_.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), q.data_ptr(),
+                                             self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st),
+                       "htr_dec_rope_cache")
+            _lib.check(L_.htr_dec_attention(q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), pos.data_ptr(),
+                                            att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_attention")
+            ops.linear_fused(att.view(T, c.q_heads * c.head_dim), *L["o"], out=x, residual=True)
+            gu = ops.linear_fused(x, *L["gate_up"], prologue=ops.PROLOGUE_RMSNORM, norm_weight=L["ln2"], eps=c.eps)
+            ops.linear_fused(gu, *L["down"], out=x, prologue=ops.PROLOGUE_SWIGLU, residual=True)
+        return ops.linear_fused(x, *self.head, prologue=ops.PROLOGUE_RMSNORM, norm_weight=self.ln_f, eps=c.eps)
 
     def forward(self, ids, pos):
         """ids [T] token ids, pos [T] their positions (device tensors).  Returns logits [T, vocab] and updates the cache."""

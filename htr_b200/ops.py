@@ -130,6 +130,43 @@ def linear_padded(x, qweight, scales, su, sv, bias=None, m_out=None):
     return y.reshape(*x.shape[:-1], m_out)
 
 
+PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_SWIGLU = 0, 1, 2
+
+
+def linear_fused(x2, qweight, scales, su, sv, out=None, prologue=PROLOGUE_NONE, norm_weight=None, eps=0.0, residual=False):
+    """GEMV with the element-wise neighbours of a decoder layer folded in (bf16, at most 8 rows; `htr_linear_fused`):
+
+      prologue=PROLOGUE_RMSNORM  the linear sees rmsnorm(x2) * norm_weight
+      prologue=PROLOGUE_SWIGLU   x2 is [rows, 2n] = [gate | up]; the linear sees silu(gate) * up
+      residual=True              `out` is the residual stream [rows, m]: out += result, in place
+
+    Returns `out` (allocated when not given and residual is False).  The reference runs these steps as separate kernels of its
+    serving stack; results equal the unfused bf16 operators up to the summation order of the norm."""
+    if x2.dtype != torch.bfloat16 or not x2.is_cuda or x2.dim() != 2:
+        raise _lib.HTRError("htr_linear_fused: activations must be a 2-D bf16 CUDA tensor")
+    M = x2.shape[0]
+    mt, nt, W = qweight.shape
+    K = W // 8
+    cols = nt * 16 * (2 if prologue == PROLOGUE_SWIGLU else 1)
+    if x2.shape[1] != cols or M > GEMV_MAX_M or not x2.is_contiguous():
+        raise _lib.HTRError(f"htr_linear_fused: activations must be contiguous [rows <= {GEMV_MAX_M}, {cols}]")
+    if out is None:
+        if residual:
+            raise _lib.HTRError("htr_linear_fused: residual=True needs the residual stream as `out`")
+        out = torch.empty((M, mt * 16), dtype=x2.dtype, device=x2.device)
+    elif out.dtype != x2.dtype or tuple(out.shape) != (M, mt * 16) or not out.is_contiguous():
+        raise _lib.HTRError("htr_linear_fused: `out` must be a contiguous bf16 [rows, m] tensor")
+    if M == 0:
+        return out
+    with torch.cuda.device(x2.device):
+        ws = workspace(x2.device, _lib.lib.htr_linear_workspace_bytes(M, mt * 16, nt * 16, K))
+        rc = _lib.lib.htr_linear_fused(x2.data_ptr(), M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(), sv.data_ptr(),
+                                       out.data_ptr(), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(x2.device).cuda_stream,
+                                       int(prologue), None if norm_weight is None else norm_weight.data_ptr(), float(eps), int(bool(residual)))
+        _lib.check(rc, "htr_linear_fused")
+    return out
+
+
 _GEMM_WS = {}
 
 

@@ -124,6 +124,19 @@ int htr_linear_padded(const void* x, int dtype, int M, int n_in, const void* qwe
                       const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* workspace,
                       size_t workspace_bytes, htr_stream_t stream);
 
+/* Decoder fusions of the GEMV (bf16 activations, M <= HTR_GEMV_MAX_ROWS, no bias; no counterpart in the reference, whose serving
+ * stack runs these element-wise steps as separate kernels around HTRLinearMethod.apply, htr/vllm_plugin.py:130-138):
+ *   prologue HTR_PROLOGUE_RMSNORM : the linear's input is rmsnorm(x) * norm_weight (row-wise over the n columns, eps), x[M][n]
+ *   prologue HTR_PROLOGUE_SWIGLU  : x holds [gate | up] rows of 2n values; the linear's input is silu(gate) * up
+ *   residual 1                    : y[M][m] is the residual stream, y <- y + result (in place) instead of y <- result
+ * Intermediate values are rounded to bf16 exactly where the unfused bf16 operators round them. */
+#define HTR_PROLOGUE_NONE 0
+#define HTR_PROLOGUE_RMSNORM 1
+#define HTR_PROLOGUE_SWIGLU 2
+int htr_linear_fused(const void* x, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                     const uint8_t* sv, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream, int prologue,
+                     const void* norm_weight, float eps, int residual);
+
 /* Tensor-core form of the packed linear for prefill-sized batches, 1 <= M <= HTR_GEMM_MAX_ROWS rows per call:
  * decoded tiles go straight into the shared-memory operand of tcgen05.mma, accumulators live in TMEM; two launches
  * (activation transform to fp16 hi/lo planes, then the GEMM with the same split reduction and epilogue as the GEMV).

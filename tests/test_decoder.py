@@ -54,3 +54,50 @@ def test_small_decoder_matches_dense_evaluation():
     agree = (pred == toks).float().mean().item()
     assert agree >= 0.75, agree                                 # bf16 chain vs float32: near-ties may flip, most tokens agree
     assert model.packed_bytes_per_token() > 0 and t_decode > 0
+
+
+@pytest.mark.parametrize("K", (2, 3, 4, 5))
+@pytest.mark.parametrize("rows", (1, 3, 8))
+def test_folded_gemv_forms_equal_the_separate_kernels(K, rows, monkeypatch):
+    """htr_linear_fused against glue kernel + htr_linear: SwiGLU prologue and residual epilogue bit for bit, RMSNorm prologue
+    up to the summation order of the row's mean square (<= 1 bf16 ulp on a few inputs)."""
+    from htr_b200 import _lib, ops, wire
+
+    monkeypatch.setattr(ops, "GEMV_ROUTE_MAX", 8)
+    dev = torch.device("cuda:0")
+    st = torch.cuda.current_stream(dev).cuda_stream
+    n, m = 512, 384
+    g = torch.Generator().manual_seed(10 * K + rows)
+    w = wire.random_packed(m, n, K, seed=K + rows, device=dev)
+    x = torch.randn(rows, n, generator=g).bfloat16().to(dev)
+    gamma = (1.0 + 0.1 * torch.randn(n, generator=g)).bfloat16().to(dev)
+    # RMSNorm folded into the activation staging
+    h = torch.empty_like(x)
+    resid = x.clone()
+    _lib.check(_lib.lib.htr_dec_add_rmsnorm(resid.data_ptr(), None, gamma.data_ptr(), h.data_ptr(), rows, n, 1e-6, st), "htr_dec_add_rmsnorm")
+    want = ops.linear(h, *w)
+    got = ops.linear_fused(x, *w, prologue=ops.PROLOGUE_RMSNORM, norm_weight=gamma, eps=1e-6)
+    assert float((got.float() - want.float()).norm() / want.float().norm()) <= 2e-3
+    assert float((got != want).float().mean()) <= 0.05
+    # SwiGLU folded into the activation staging: x = [gate | up]
+    w2 = wire.random_packed(m, n, K, seed=50 + K + rows, device=dev)
+    gu = torch.randn(rows, 2 * n, generator=g).bfloat16().to(dev)
+    act = torch.empty(rows, n, dtype=torch.bfloat16, device=dev)
+    _lib.check(_lib.lib.htr_dec_swiglu(gu.data_ptr(), act.data_ptr(), rows, n, st), "htr_dec_swiglu")
+    assert torch.equal(ops.linear_fused(gu, *w2, prologue=ops.PROLOGUE_SWIGLU), ops.linear(act, *w2))
+    # residual epilogue: out += result, in place
+    stream = torch.randn(rows, m, generator=g).bfloat16().to(dev)
+    want = stream + ops.linear(x, *w)
+    out = stream.clone()
+    assert ops.linear_fused(x, *w, out=out, residual=True) is out and torch.equal(out, want)
+    # both at once, as the down projection uses them
+    want = stream + ops.linear(act, *w2)
+    out = stream.clone()
+    ops.linear_fused(gu, *w2, out=out, prologue=ops.PROLOGUE_SWIGLU, residual=True)
+    assert torch.equal(out, want)
+    with pytest.raises(_lib.HTRError):
+        ops.linear_fused(x.float(), *w)
+    with pytest.raises(_lib.HTRError):
+        ops.linear_fused(x, *w, residual=True)
+    with pytest.raises(_lib.HTRError):
+        ops.linear_fused(x, *w, prologue=ops.PROLOGUE_RMSNORM)          # no norm weight
