@@ -20,6 +20,8 @@ repository's code.  Fixtures:
   viterbi.npz       htr/reference.py viterbi (the encoder's trellis search) on seeded tiles: targets, weights, the states it
                     returns and their cost, K2..K5 tail-biting + K4 without tail-biting + K6/K8 on one tile
                     (only with --viterbi, it takes a few minutes)
+  encode_K3.npz     htr/encode.py encode_group on a 128x256 matrix with an outlier-channel Hessian, inputs included
+                    (W, H), two members sharing the input signs (only with --encode)
 """
 import argparse
 import hashlib
@@ -37,6 +39,7 @@ def main():
     ap.add_argument("--reference", required=True, help="path of the HTR checkout")
     ap.add_argument("--out", default=HERE)
     ap.add_argument("--viterbi", action="store_true", help="write viterbi.npz only")
+    ap.add_argument("--encode", action="store_true", help="write encode_K3.npz only")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from htr import encode, wire
@@ -45,6 +48,8 @@ def main():
     out = a.out
     if a.viterbi:
         return viterbi_fixture(out)
+    if a.encode:
+        return encode_fixture(out)
 
     # ---- codebook
     v = wire.gen_values(torch.arange(65536))
@@ -122,6 +127,32 @@ def main():
     finally:
         encode.VITERBI = old
     print("wrote fixtures to", out)
+
+
+def encode_fixture(out):
+    """A group of two matrices that share their input (as gate/up or q/k/v members do), encoded by the reference."""
+    from htr import encode
+
+    g = torch.Generator().manual_seed(4242)
+    n = 256
+    X = torch.randn(512, n, generator=g)
+    X[:, torch.randperm(n, generator=g)[:3]] *= 10.0
+    H = X.T @ X / X.shape[0]
+    Ws = [torch.randn(128, n, generator=g) * 0.02, torch.randn(256, n, generator=g) * 0.03]
+    old, encode.VITERBI = encode.VITERBI, None
+    try:
+        res = encode.encode_group([{"W": w, "H": H} for w in Ws], 3, seed=1234, max_batch=64)
+    finally:
+        encode.VITERBI = old
+    d = {"H": H.numpy()}
+    for i, (w, r) in enumerate(zip(Ws, res)):
+        err = (w - r["What"]).double()
+        d[f"W{i}"], d[f"qweight{i}"], d[f"scales{i}"] = w.numpy(), r["qweight"].numpy(), r["scales"].numpy()
+        d[f"su{i}"], d[f"sv{i}"] = r["su"].numpy(), r["sv"].numpy()          # What = wire.dequant of these four (htr/encode.py:103-105)
+        d[f"proxy{i}"] = np.float64(torch.trace(err @ H.double() @ err.T))
+        print(i, "proxy loss", float(d[f"proxy{i}"]))
+    np.savez_compressed(os.path.join(out, "encode_K3.npz"), **d)
+    print("wrote", os.path.join(out, "encode_K3.npz"))
 
 
 def viterbi_fixture(out):
