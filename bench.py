@@ -16,7 +16,8 @@ One JSON line is printed by rank 0:
             independent, so they are launched with HTR_LINEAR_INPUT_INDEPENDENT (consecutive launches overlap);
             `stream_ordered` repeats the pass in the default form, in which each launch waits for its predecessor
   e2e       the same pass through the public operator (htr_b200.ops.linear) with the activations in pinned
-            host memory and the outputs copied back to pinned host memory inside the timed region
+            host memory and the outputs copied back to pinned host memory inside the timed region (one host->device
+            copy of a K-group's activations before its linears, one device->host copy of its outputs after them)
   roofline  of the GEMV kernel: achieved = algorithmic packed bytes per launch / average launch duration,
             peak = measured HBM copy bandwidth (MEASURED_PEAKS.json, else the fallback 6650 GB/s)
   cpu_baseline  the CPU restatement of the reference's decode + matmul path (oracle/, OpenMP) on a bounded
@@ -199,11 +200,23 @@ def run_ours(args):
                 x = torch.randn(1, n, device=dev, generator=g).bfloat16()
                 items.append(dict(x=x, w=(qw, sc, su, sv), m=m, n=n,
                                   gathered=torch.empty(world, m, dtype=torch.bfloat16, device=dev) if world > 1 else None,
-                                  xh=x.cpu().pin_memory(), xd=torch.empty_like(x),
-                                  yh=torch.empty(max(world, 1), m, dtype=torch.bfloat16).pin_memory()))
+                                  xd=None))
                 total_bytes += payload_bytes(m, n, K)
                 launches += 1
         groups.append(items)
+    # end-to-end form: the activations of a K-group travel in one host->device copy (pinned pool), its outputs in one
+    # device->host copy; the items hold views of the pools
+    for items in groups:
+        n_in = sum(it["n"] for it in items)
+        n_out = sum(max(world, 1) * it["m"] for it in items)
+        xh_pool, xd_pool = torch.empty(n_in, dtype=torch.bfloat16).pin_memory(), torch.empty(n_in, dtype=torch.bfloat16, device=dev)
+        yh_pool, yd_pool = torch.empty(n_out, dtype=torch.bfloat16).pin_memory(), torch.empty(n_out, dtype=torch.bfloat16, device=dev)
+        at = 0
+        for it in items:
+            xh_pool[at:at + it["n"]].copy_(it["x"].view(-1).cpu())
+            it["xd"] = xd_pool[at:at + it["n"]].view(1, it["n"])
+            at += it["n"]
+        items[0]["pools"] = (xh_pool, xd_pool, yh_pool, yd_pool)
     # N > 1: every rank's epilogue stores its rows into all ranks' gather buffers (symmetric memory, plain NVLink stores);
     # one cross-rank barrier per K-group orders the ranks.  HTR_BENCH_GATHER=nccl uses NCCL all-gathers on a side stream instead.
     side = torch.cuda.Stream(device=dev)
@@ -226,9 +239,11 @@ def run_ours(args):
 
     def run_group(items, from_host=False):
         main = torch.cuda.current_stream()
+        xh_pool, xd_pool, yh_pool, yd_pool = items[0]["pools"]
+        if from_host:
+            xd_pool.copy_(xh_pool, non_blocking=True)
+        outs = []
         for it in items:
-            if from_host:
-                it["xd"].copy_(it["xh"], non_blocking=True)
             xin = it["xd"] if from_host else it["x"]
             if gather_mode == "peer":
                 ops.linear_into_peers(xin, *it["w"], None, it["peers"], rank * it["m"])
@@ -238,18 +253,18 @@ def run_ours(args):
                 side.wait_stream(main)
                 with torch.cuda.stream(side):
                     dist.all_gather_into_tensor(it["gathered"], y)
-                    if from_host:
-                        it["yh"].copy_(it["gathered"], non_blocking=True)
                 y.record_stream(side)
-            elif from_host:
-                it["yh"].copy_(y, non_blocking=True)
+                outs.append(it["gathered"].view(-1))
+            else:
+                outs.append(y.view(-1))
         if gather_mode == "nccl":
             main.wait_stream(side)
         if gather_mode == "peer":
             hdl.barrier(channel=0)
-            if from_host:
-                for it in items:
-                    it["yh"].copy_(it["gathered"], non_blocking=True)
+            outs = [it["gathered"].view(-1) for it in items]
+        if from_host:
+            torch.cat(outs, out=yd_pool)
+            yh_pool.copy_(yd_pool, non_blocking=True)
 
     # warm every kernel, the workspace and NCCL, then capture CUDA graphs (one per K-group and launch form)
     for items in groups:
@@ -321,10 +336,10 @@ def run_ours(args):
     ov_ms, ov_per_k_ms = timed(capture() if use_graphs else None, args.steps)
     # end to end through the public operator: activations from pinned host memory, outputs back to pinned host memory
     e2e_steps = max(1, min(args.steps, 10))
-    e2e_ms, _ = timed(capture(from_host=True) if use_graphs else None, e2e_steps, from_host=True)
+    e2e_ms, _ = timed(capture(independent=True, from_host=True) if use_graphs else None, e2e_steps, from_host=True, independent=True)
     clocks = sampler.stop() if rank == 0 else None
-    h2d = sum(it["xh"].numel() * 2 for items in groups for it in items)
-    d2h = sum((it["gathered"].numel() if it["gathered"] is not None else it["m"]) * 2 for items in groups for it in items)
+    h2d = sum(items[0]["pools"][0].numel() * 2 for items in groups)
+    d2h = sum(items[0]["pools"][2].numel() * 2 for items in groups)
 
     if world > 1:
         t = torch.tensor([ms, e2e_ms, ov_ms] + per_k_ms + ov_per_k_ms, device=dev, dtype=torch.float64)
