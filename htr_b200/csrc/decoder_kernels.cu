@@ -157,6 +157,83 @@ __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __r
   out[((size_t)t * hq + head) * D + tid] = __float2bfloat16_rn(acc / sum);
 }
 
+// Single-token step: rotary embedding, cache write and attention of one query head in one kernel.  grid (heads_q), 128 threads,
+// D == 128.  The CTA rotates its query and its group's new key itself (the four query heads of a group repeat that small piece
+// of work), takes the scores and values of the new position from shared memory and those of older positions from the cache;
+// the first head of each group writes the new key and value rows.  Same roundings as rope_cache_kernel + attention_kernel.
+__global__ void __launch_bounds__(128) rope_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ pos,
+                                                             const float* __restrict__ cosv, const float* __restrict__ sinv,
+                                                             __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                                             __nv_bfloat16* __restrict__ out, int hq, int hkv) {
+  constexpr int D = 128;
+  __shared__ __align__(16) float sq[D];
+  __shared__ float sk[D], sv[D];
+  __shared__ float sc[HTR_DEC_MAX_LEN];
+  __shared__ float red[4];
+  pdl_enter();
+  const int head = blockIdx.x, tid = threadIdx.x;
+  const int rep = hq / hkv, kvh = head / rep;
+  const int p = (int)pos[0], len = p + 1;
+  {
+    const int i = tid >> 1;                                               // pair (2i, 2i+1); even threads own the first element
+    const float c = cosv[(size_t)p * (D / 2) + i], s = sinv[(size_t)p * (D / 2) + i];
+    const float2 qv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qkv + (size_t)head * D + 2 * i));
+    const float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qkv + (size_t)(hq + kvh) * D + 2 * i));
+    const __nv_bfloat16 qr = __float2bfloat16_rn((tid & 1) ? qv.x * s + qv.y * c : qv.x * c - qv.y * s);
+    const __nv_bfloat16 kr = __float2bfloat16_rn((tid & 1) ? kv.x * s + kv.y * c : kv.x * c - kv.y * s);
+    const __nv_bfloat16 vn = qkv[(size_t)(hq + hkv + kvh) * D + tid];
+    sq[tid] = bf(qr) * 0.08838834764831845f;                              // 1/sqrt(128)
+    sk[tid] = bf(kr);
+    sv[tid] = bf(vn);
+    if (head == kvh * rep) {
+      k_cache[((size_t)p * hkv + kvh) * D + tid] = kr;
+      v_cache[((size_t)p * hkv + kvh) * D + tid] = vn;
+    }
+  }
+  __syncthreads();
+  float mx = -3.0e38f;
+  for (int t = tid; t < len; t += 128) {
+    float d = 0.f;
+    if (t == p) {
+#pragma unroll 8
+      for (int e = 0; e < D; ++e) d += sk[e] * sq[e];
+    } else {
+      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + ((size_t)t * hkv + kvh) * D);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const uint4 raw = __ldg(kr + c);
+        const float4 q0 = *reinterpret_cast<const float4*>(sq + 8 * c), q1 = *reinterpret_cast<const float4*>(sq + 8 * c + 4);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z)), f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+        d += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + e.x * q1.x + e.y * q1.y + f.x * q1.z + f.y * q1.w;
+      }
+    }
+    sc[t] = d;
+    mx = fmaxf(mx, d);
+  }
+  mx = block_max(mx, red);
+  float sum = 0.f;
+  for (int t = tid; t < len; t += 128) {
+    const float e = __expf(sc[t] - mx);
+    sc[t] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  const __nv_bfloat16* vcol = v_cache + (size_t)kvh * D + tid;
+  float acc = 0.f;
+  int t = 0;
+  for (; t + 8 <= p; t += 8) {
+    float vv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) vv[j] = bf(vcol[(size_t)(t + j) * hkv * D]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += sc[t + j] * vv[j];
+  }
+  for (; t < p; ++t) acc += sc[t] * bf(vcol[(size_t)t * hkv * D]);
+  acc += sc[p] * sv[tid];
+  out[(size_t)head * D + tid] = __float2bfloat16_rn(acc / sum);
+}
+
 // out = silu(gate) * up, gu = [T, 2I] with the gate half first
 __global__ void __launch_bounds__(256) swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int I, int total) {
   pdl_enter();
@@ -218,6 +295,17 @@ int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, c
   const int e = launch_pdl(attention_kernel, dim3(q_heads, rows), dim3(128), static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(q),
                            static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
                            reinterpret_cast<const long long*>(pos), static_cast<__nv_bfloat16*>(out), q_heads, kv_heads);
+  return e ? HTR_ERR_CUDA : HTR_OK;
+}
+
+int htr_dec_rope_attention(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* k_cache, void* v_cache, void* out,
+                           int q_heads, int kv_heads, int head_dim, htr_stream_t stream) {
+  if (!qkv || !pos || !cosv || !sinv || !k_cache || !v_cache || !out) return HTR_ERR_NULL;
+  if (head_dim != 128 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return HTR_ERR_BAD_SHAPE;
+  const int e = launch_pdl(rope_attention_kernel, dim3(q_heads), dim3(128), static_cast<cudaStream_t>(stream),
+                           static_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const long long*>(pos), cosv, sinv,
+                           static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(out), q_heads,
+                           kv_heads);
   return e ? HTR_ERR_CUDA : HTR_OK;
 }
 

@@ -222,7 +222,7 @@ class PackedDecoder:
 
     def forward_folded(self, ids, pos):
         """Decode-sized step (at most 8 rows) with the norms, the SwiGLU and the residual adds folded into the packed GEMVs
-        (`ops.linear_fused`): six launches per layer instead of nine."""
+        (`ops.linear_fused`): six launches per layer instead of nine, five for a single token."""
         c, L_ = self.cfg, _lib.lib
         T = ids.shape[0]
         dev = self.device
@@ -232,11 +232,16 @@ class PackedDecoder:
         att = torch.empty_like(q)
         for li, L in enumerate(self.layers):
             qkv = ops.linear_fused(x, *L["qkv"], prologue=ops.PROLOGUE_RMSNORM, norm_weight=L["ln1"], eps=c.eps)
-            _lib.check(L_.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), q.data_ptr(),
-                                             self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st),
-                       "htr_dec_rope_cache")
-            _lib.check(L_.htr_dec_attention(q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), pos.data_ptr(),
-                                            att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_attention")
+            if T == 1:                                          # one token: rotary embedding, cache write and attention in one launch
+                _lib.check(L_.htr_dec_rope_attention(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
+                                                     self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), att.data_ptr(),
+                                                     c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_rope_attention")
+            else:
+                _lib.check(L_.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), q.data_ptr(),
+                                                 self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st),
+                           "htr_dec_rope_cache")
+                _lib.check(L_.htr_dec_attention(q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), pos.data_ptr(),
+                                                att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_attention")
             ops.linear_fused(att.view(T, c.q_heads * c.head_dim), *L["o"], out=x, residual=True)
             gu = ops.linear_fused(x, *L["gate_up"], prologue=ops.PROLOGUE_RMSNORM, norm_weight=L["ln2"], eps=c.eps)
             ops.linear_fused(gu, *L["down"], out=x, prologue=ops.PROLOGUE_SWIGLU, residual=True)

@@ -174,6 +174,9 @@ int htr_dec_rope_cache(const void* qkv, const int64_t* pos, const float* cosv, c
 int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int rows, int q_heads,
                       int kv_heads, int head_dim, htr_stream_t stream);
 int htr_dec_swiglu(const void* gate_up, void* out, int rows, int intermediate, htr_stream_t stream);
+/* rope_cache + attention of a single-token step (one row) in one launch: the same values, the new key/value rows written once */
+int htr_dec_rope_attention(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* k_cache, void* v_cache,
+                           void* out, int q_heads, int kv_heads, int head_dim, htr_stream_t stream);
 
 /* Encoder-side search: tail-biting Viterbi over the bit-shift trellis, one tile per row of x[B][T] with weights w[B][T]
  * (float32, T <= 256; the encoder uses T = 256).  Replaces htr/reference.py:7-50 (viterbi) and the CUDA module of

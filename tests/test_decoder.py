@@ -101,3 +101,31 @@ def test_folded_gemv_forms_equal_the_separate_kernels(K, rows, monkeypatch):
         ops.linear_fused(x, *w, residual=True)
     with pytest.raises(_lib.HTRError):
         ops.linear_fused(x, *w, prologue=ops.PROLOGUE_RMSNORM)          # no norm weight
+
+
+def test_single_token_rope_attention_equals_the_two_kernels():
+    from htr_b200 import _lib
+
+    dev = torch.device("cuda:0")
+    L = _lib.lib
+    st = torch.cuda.current_stream(dev).cuda_stream
+    hq, hkv, D, max_len = 8, 2, 128, 300
+    g = torch.Generator().manual_seed(3)
+    inv = 1.0 / (1.0e6 ** (torch.arange(0, D, 2).float() / D))
+    ang = torch.arange(max_len).float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(dev), ang.sin().to(dev)
+    for p in (0, 1, 7, 130, 299):
+        kc = torch.randn(max_len, hkv, D, generator=g).bfloat16().to(dev)
+        vc = torch.randn(max_len, hkv, D, generator=g).bfloat16().to(dev)
+        qkv = torch.randn(1, (hq + 2 * hkv) * D, generator=g).bfloat16().to(dev)
+        pos = torch.full((1,), p, dtype=torch.long, device=dev)
+        k1, v1, k2, v2 = kc.clone(), vc.clone(), kc.clone(), vc.clone()
+        q = torch.empty(1, hq, D, dtype=torch.bfloat16, device=dev)
+        want, got = torch.empty_like(q), torch.empty_like(q)
+        _lib.check(L.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k1.data_ptr(), v1.data_ptr(),
+                                        1, hq, hkv, D, st), "htr_dec_rope_cache")
+        _lib.check(L.htr_dec_attention(q.data_ptr(), k1.data_ptr(), v1.data_ptr(), pos.data_ptr(), want.data_ptr(), 1, hq, hkv, D, st), "htr_dec_attention")
+        _lib.check(L.htr_dec_rope_attention(qkv.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), k2.data_ptr(), v2.data_ptr(), got.data_ptr(),
+                                            hq, hkv, D, st), "htr_dec_rope_attention")
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)                 # the same cache rows
+        assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
