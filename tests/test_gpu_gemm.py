@@ -35,6 +35,24 @@ def test_gemm_matches_oracle(coracle, K, m, n, M):
     assert yb.dtype == torch.bfloat16 and rel(yb.float().cpu().numpy(), refb) <= 4e-3
 
 
+@pytest.mark.parametrize("K,m,n,M", ((4, 20480, 512, 64), (3, 12288, 1024, 100), (5, 24576, 256, 16)))
+def test_gemm_when_ctas_cross_row_blocks(coracle, K, m, n, M):
+    """Tall matrices: more row blocks than resident CTAs, so the (row block, column block) units are dealt in even runs and a CTA
+    may finish one row block and start the next (two passes of the pipeline, barriers re-initialised in between)."""
+    from htr_b200 import ops, wire
+
+    dev = torch.device("cuda:0")
+    qw, sc, su, sv = wire.random_packed(m, n, K, seed=K + M)
+    x = torch.randn(M, n, generator=torch.Generator().manual_seed(M)).bfloat16()
+    ref = coracle.linear(x.float().numpy(), qw.numpy(), sc.numpy(), su.numpy(), sv.numpy())
+    d = [t.to(dev) for t in (qw, sc, su, sv)]
+    y = ops.linear(x.to(dev), *d)
+    assert rel(y.float().cpu().numpy(), ref) <= 4e-3
+    assert torch.equal(ops.linear(x.to(dev), *d), y) and all(c == 0 for c in ops.gemm_error_codes())
+    yf = ops.linear(x.float().to(dev), *d)
+    assert rel(yf.cpu().numpy(), ref) <= 5e-5
+
+
 def test_gemm_full_size_and_bit_stability(coracle):
     from htr_b200 import ops, wire
 
