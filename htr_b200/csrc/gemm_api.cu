@@ -125,7 +125,7 @@ constexpr size_t kCounterRegion = 1 << 16;   // same fixed counter region as the
 constexpr size_t kErrorRegion = 256;
 
 struct GemmPlan {
-  int np, rbs, hb, split, grid, slots, stages;
+  int np, rbs, hb, split, grid, stages;
   size_t off_xb, off_xsum, off_tok, off_part, total;
 };
 
@@ -176,33 +176,16 @@ int make_gemm_plan(int M, int m, int n, int K, int planes, GemmPlan* out) {
     }
   }
   if (!found) return HTR_ERR_TOO_LARGE;
-  // decomposition: CTAs per row block when that fills the GPU evenly, else even runs of (row block, 128-column block) units
-  const long long cap = (long long)sms * per_sm, units = (long long)g.rbs * g.hb;
-  long long s = cap / g.rbs;
+  long long s = (long long)sms * per_sm / g.rbs;
   if (s < 1) s = 1;
   if (s > g.hb) s = g.hb;
-  const long long split_grid = g.rbs * s;
-  const long long split_span = ((split_grid + cap - 1) / cap) * ((g.hb + s - 1) / s);     // 128-column blocks on the busiest SM slot
-  const long long flat_grid = units < cap ? units : cap;
-  const long long flat_span = (units + flat_grid - 1) / flat_grid + 1;                     // + the cost of crossing a row block
-#ifndef HTR_GEMM_FLAT
-#define HTR_GEMM_FLAT 1
-#endif
-  if (HTR_GEMM_FLAT && flat_span < split_span) {
-    g.split = 0;
-    g.grid = (int)flat_grid;
-    const long long run = units / flat_grid;                                               // shortest run of a CTA
-    g.slots = (int)((g.hb + run - 1) / run) + 1;
-  } else {
-    g.split = (int)s;
-    g.grid = (int)split_grid;
-    g.slots = (int)s;
-  }
+  g.split = (int)s;
+  g.grid = g.rbs * g.split;
   size_t off = kCounterRegion + kErrorRegion;
   g.off_xb = off; off += align256((size_t)ncols * n * 2);
   g.off_xsum = off; off += align256((size_t)g.np * gemm_rht_slices(g.np, n) * 4);
   g.off_tok = off; off += align256((size_t)g.np * 4);
-  g.off_part = off; off += align256((size_t)g.rbs * g.slots * g.np * 128 * 4);
+  g.off_part = off; off += align256((size_t)g.rbs * g.split * g.np * 128 * 4);
   g.total = off;
   *out = g;
   return HTR_OK;
@@ -281,7 +264,6 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
   p.dtype = dtype;
   p.hb = g.hb;
   p.split = g.split;
-  p.slots = g.slots;
   p.stages = g.stages;
   p.xsum_slices = gemm_rht_slices(g.np, n);
   p.cb = (float)codebook_scale();

@@ -86,9 +86,7 @@ struct GemmParams {
   int mt, nt;
   int dtype;
   int hb;                 // 128-column blocks per row (n / 128) = units per row block
-  int split;              // > 0: every row block is shared by exactly `split` CTAs (grid = row blocks * split); 0: the (row block,
-                          // 128-column block) units are dealt to the CTAs in even contiguous runs, which may cross a row block
-  int slots;              // partial-sum slots per row block
+  int split;              // CTAs per row block
   int stages;             // stage pairs in the ring (2..kMaxStages)
   int xsum_slices;
   float cb;
@@ -213,7 +211,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
 }
 
 template <int K>
-__global__ void __launch_bounds__(kGemmThreads, 2) packed_gemm_tc_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const GemmParams p) {
   extern __shared__ __align__(128) unsigned char gsm[];
   __shared__ __align__(8) unsigned long long s_afull[kMaxStages], s_bfull[kMaxStages], s_freed[kMaxStages], s_done;
   __shared__ uint32_t s_tmem;
@@ -225,17 +223,9 @@ __global__ void __launch_bounds__(kGemmThreads, 2) packed_gemm_tc_kernel(const G
   HTR_GTRACE(tid == 0, 0);
   const int np = p.np, ncols = p.planes * np;               // accumulator columns: hi plane, then lo plane if present
   const int nt = p.nt, m = p.mt * 16, HB = p.hb, NS = p.stages;
-  // this CTA's run of units u = row block * HB + 128-column block; a segment = the part of the run inside one row block
-  const long long U = (long long)(p.mt / 8) * HB, G = gridDim.x;
-  long long u_begin, u_end;
-  if (p.split > 0) {
-    const int brb = blockIdx.x / p.split, part = blockIdx.x - brb * p.split;
-    u_begin = (long long)brb * HB + (long long)part * HB / p.split;
-    u_end = (long long)brb * HB + (long long)(part + 1) * HB / p.split;
-  } else {
-    u_begin = (long long)blockIdx.x * U / G;
-    u_end = ((long long)blockIdx.x + 1) * U / G;
-  }
+  const int rb = blockIdx.x / p.split, part_id = blockIdx.x - rb * p.split;
+  const int hb_begin = part_id * HB / p.split, hb_end = (part_id + 1) * HB / p.split;
+  const int chunks = (hb_end - hb_begin) * 2;                // two 64-column chunks per 128-column block
   constexpr int kStripBytes = 4 * 32 * K, R = gemm_raw_slots(K);
   const int b_tile_bytes = ncols * 128, stage_bytes = kDecodeGroups * (kATileBytes + b_tile_bytes);   // pair: A0 | A1 | B0 | B1
   unsigned char* stage0 = gsm + (128 - (smem_u32(gsm) & 127)) % 128;   // 128-byte aligned start: stage s = {A tile, B tile}
@@ -244,30 +234,19 @@ __global__ void __launch_bounds__(kGemmThreads, 2) packed_gemm_tc_kernel(const G
 
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < ncols) tmem_cols <<= 1;
-  if (tid == 0) s_fail = 0;
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-
-  for (long long u = u_begin; u < u_end;) {
-  const int rb = (int)(u / HB), hb_begin = (int)(u - (long long)rb * HB);
-  const int hb_end = (int)((long long)hb_begin + (u_end - u) < (long long)HB ? (long long)hb_begin + (u_end - u) : (long long)HB);
-  const int chunks = (hb_end - hb_begin) * 2;                // two 64-column chunks per 128-column block
-  if (tid == 0) {                                            // fresh barriers for every segment (all threads are past the last one)
+  if (tid == 0) {
     for (int s = 0; s < kMaxStages; ++s) {
-      if (u != u_begin) {
-        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&s_afull[s])) : "memory");
-        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&s_bfull[s])) : "memory");
-        asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&s_freed[s])) : "memory");
-      }
       mbar_init(smem_u32(&s_afull[s]), kGemmDecodeWarps);              // one arrival per decode warp (both groups)
       mbar_init(smem_u32(&s_bfull[s]), 1);                             // the B lane's arrive.expect_tx
       mbar_init(smem_u32(&s_freed[s]), 1);                             // tcgen05.commit
     }
-    if (u != u_begin) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&s_done)) : "memory");
     mbar_init(smem_u32(&s_done), 1);
+    s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
 
   if (warp < kGemmDecodeWarps) {
@@ -462,20 +441,13 @@ __global__ void __launch_bounds__(kGemmThreads, 2) packed_gemm_tc_kernel(const G
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   HTR_GTRACE(tid == 0, 3);
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
 
   // ---- split reduction across the CTAs of this row block (same scheme as the GEMV), then the epilogue
   bool finish = true;
-  int first, contributors;                                   // the CTAs that share row block rb, in slot order
-  if (p.split > 0) {
-    first = rb * p.split;
-    contributors = p.split;
-  } else {
-    first = (int)((((long long)rb * HB + 1) * G - 1) / U);   // owner of a unit x when CTA b starts at floor(b * U / G)
-    contributors = (int)(((((long long)rb + 1) * HB) * G - 1) / U) - first + 1;
-  }
-  const int part_id = (int)blockIdx.x - first;
+  const int contributors = p.split;
   if (contributors > 1) {
-    float4* mine = reinterpret_cast<float4*>(p.part + ((size_t)rb * p.slots + part_id) * ((size_t)np * 128));
+    float4* mine = reinterpret_cast<float4*>(p.part + ((size_t)rb * contributors + part_id) * ((size_t)np * 128));
     for (int e = tid; e < np * 32; e += kGemmThreads) __stcg(mine + e, reinterpret_cast<const float4*>(result)[e]);
     __syncthreads();
     if (tid == 0) {
@@ -487,7 +459,7 @@ __global__ void __launch_bounds__(kGemmThreads, 2) packed_gemm_tc_kernel(const G
     finish = (s_arrival == contributors - 1);
     HTR_GTRACE(tid == 0, 4);
     if (finish) {
-      const float4* slot0 = reinterpret_cast<const float4*>(p.part + (size_t)rb * p.slots * ((size_t)np * 128));
+      const float4* slot0 = reinterpret_cast<const float4*>(p.part + (size_t)rb * contributors * ((size_t)np * 128));
       for (int e = tid; e < np * 32; e += kGemmThreads) {
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int sl = 0; sl < contributors; ++sl) {
@@ -500,33 +472,27 @@ __global__ void __launch_bounds__(kGemmThreads, 2) packed_gemm_tc_kernel(const G
     }
     __syncthreads();
   }
-  if (finish) {
-    // epilogue: one warp per activation row j; lane holds rows 4*lane .. 4*lane+3 of the block
-    const int row0 = rb * 128 + 4 * lane;
-    const uint2 sc_raw = __ldg(reinterpret_cast<const uint2*>(p.scales + row0));
-    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.y));
-    const unsigned sv_bits = sign_nibble(p.sv, rb * 32 + lane);
-    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
-    HTR_GTRACE(tid == 0, 5);
-    for (int j = warp; j < p.rows; j += kGemmWarps) {
-      float xs = 0.f;
-      for (int y = 0; y < p.xsum_slices; ++y) xs += p.xsum[j * p.xsum_slices + y];   // fixed order: results do not depend on scheduling
-      const float off = 1534.0f * xs, rs = p.cb * p.tok[j];
-      const float4 r4 = *reinterpret_cast<const float4*>(result + j * 128 + 4 * lane);
-      float v[4] = {(r4.x - off) * (s01.x * rs), (r4.y - off) * (s01.y * rs), (r4.z - off) * (s23.x * rs), (r4.w - off) * (s23.y * rs)};
-      wht128(v, lane);
-      float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
-                             flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
-      o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
-      store_quad(p.y, (size_t)j * m + row0, p.dtype, o);
-    }
+  if (!finish) return;
+  // epilogue: one warp per activation row j; lane holds rows 4*lane .. 4*lane+3 of the block
+  const int row0 = rb * 128 + 4 * lane;
+  const uint2 sc_raw = __ldg(reinterpret_cast<const uint2*>(p.scales + row0));
+  const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.y));
+  const unsigned sv_bits = sign_nibble(p.sv, rb * 32 + lane);
+  float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
+  HTR_GTRACE(tid == 0, 5);
+  for (int j = warp; j < p.rows; j += kGemmWarps) {
+    float xs = 0.f;
+    for (int y = 0; y < p.xsum_slices; ++y) xs += p.xsum[j * p.xsum_slices + y];   // fixed order: results do not depend on scheduling
+    const float off = 1534.0f * xs, rs = p.cb * p.tok[j];
+    const float4 r4 = *reinterpret_cast<const float4*>(result + j * 128 + 4 * lane);
+    float v[4] = {(r4.x - off) * (s01.x * rs), (r4.y - off) * (s01.y * rs), (r4.z - off) * (s23.x * rs), (r4.w - off) * (s23.y * rs)};
+    wht128(v, lane);
+    float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
+                           flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
+    o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
+    store_quad(p.y, (size_t)j * m + row0, p.dtype, o);
   }
-  u += hb_end - hb_begin;
-  __syncthreads();                                           // the result buffer aliases the stages of the next segment
-  }  // segments
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(s_tmem), "r"(tmem_cols) : "memory");
 }
 
 int gemm_rht_slices(int np, int n);
