@@ -89,7 +89,8 @@ struct GemvParams {
   int npeer;
   long long peer_offset;
   // Grouped form (experts of a mixture-of-experts layer): group > 0 problems of identical shape, one activation row each;
-  // the per-problem tensors come from device arrays of device pointers, row blocks are numbered problem-major.
+  // the per-problem tensors come from device arrays of device pointers, row blocks are numbered problem-major.  A problem whose
+  // weight pointer is null is skipped (its output is left untouched).
   int group;
   int rb_per_problem;
   const void* const* g_x;
@@ -273,6 +274,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     rb_base = prob * p.rb_per_problem;
     x_ptr = p.g_x[prob];
     qw_ptr = p.g_qw[prob];
+    if (qw_ptr == nullptr) return;                                  // a problem this rank does not own (expert parallelism): nothing to do
     scales_ptr = p.g_scales[prob];
     su_ptr = p.g_su[prob];
     sv_ptr = p.g_sv[prob];

@@ -192,17 +192,19 @@ class ExpertParallelMoE:
         self._tables = None
 
     def _address_tables(self, dev):
-        """int64 device tensors [local experts] with the addresses of each expert's wire tensors (for the grouped kernel)."""
+        """int64 device tensors [all experts] with the addresses of each expert's wire tensors (for the grouped kernel);
+        experts of other ranks have address 0, which the kernel skips."""
         if self._tables is None:
             def col(which, i):
-                return torch.tensor([self.local[e][which][i].data_ptr() for e in range(self.first, self.first + self.count)],
+                return torch.tensor([self.local[e][which][i].data_ptr() if e in self.local else 0 for e in range(self.num_experts)],
                                     dtype=torch.int64, device=dev)
             self._tables = {w: tuple(col(w, i) for i in range(4)) for w in ("gate_up", "down")}
         return self._tables
 
     def partial_grouped(self, x, topk_ids, topk_w):
         """The same contribution with two grouped launches (gate_up, down) over all (token, slot) pairs.  Routing stays on
-        the device (no host round trip, capturable in a CUDA graph); needs every routed expert to be local."""
+        the device (no host round trip, capturable in a CUDA graph); pairs routed to another rank's experts are skipped by
+        the kernel (null weight pointer) and contribute zero here."""
         from . import ops
 
         T, hdim = x.shape
@@ -210,7 +212,7 @@ class ExpertParallelMoE:
         P = T * k
         dev = x.device
         tabs = self._address_tables(dev)
-        e_idx = (topk_ids.to(dev).reshape(-1) - self.first).to(torch.int64)
+        e_idx = topk_ids.to(dev).reshape(-1).to(torch.int64)
         gq, gs, gu_, gv = (t.index_select(0, e_idx) for t in tabs["gate_up"])
         dq, ds, du, dv = (t.index_select(0, e_idx) for t in tabs["down"])
         any_e = next(iter(self.local.values()))
@@ -220,13 +222,13 @@ class ExpertParallelMoE:
         esz = x.element_size()
         x = x.contiguous()
         tok = torch.arange(T, device=dev, dtype=torch.int64).repeat_interleave(k)
-        gu = torch.empty(P, mt_gu * 16, dtype=x.dtype, device=dev)
+        gu = torch.zeros(P, mt_gu * 16, dtype=x.dtype, device=dev)       # rows of skipped pairs stay zero
         slot = torch.arange(P, device=dev, dtype=torch.int64)
         ops.linear_grouped(x.data_ptr() + tok * (hdim * esz), gq, gs, gu_, gv, gu.data_ptr() + slot * (mt_gu * 16 * esz),
                            mt_gu, nt_gu, K, x.dtype)
         inter = mt_gu * 8
         act = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
-        dn = torch.empty(P, mt_dn * 16, dtype=x.dtype, device=dev)
+        dn = torch.zeros(P, mt_dn * 16, dtype=x.dtype, device=dev)
         ops.linear_grouped(act.data_ptr() + slot * (inter * esz), dq, ds, du, dv, dn.data_ptr() + slot * (mt_dn * 16 * esz),
                            mt_dn, nt_dn, K, x.dtype)
         return (dn.view(T, k, -1).float() * topk_w.to(device=dev, dtype=torch.float32)[:, :, None]).sum(1)
@@ -250,7 +252,7 @@ class ExpertParallelMoE:
         return out
 
     def __call__(self, x, topk_ids, topk_w, grouped=None):
-        use_grouped = (self.world == 1 and x.is_cuda) if grouped is None else grouped
+        use_grouped = (x.is_cuda and self.count > 0) if grouped is None else grouped
         part = self.partial_grouped(x, topk_ids, topk_w) if use_grouped else self.partial(x, topk_ids, topk_w)
         if self.world == 1:
             return part.to(x.dtype)

@@ -97,6 +97,8 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
  * (the experts hit by the tokens of a mixture-of-experts step).  Every list is a DEVICE array of `count` device pointers
  * (x_list[i] -> n activations, y_list[i] -> m outputs, and the four wire tensors of problem i), so that a routing kernel can
  * fill them without a host round trip; the same expert may appear several times.  count * m/128 must not exceed 16384.
+ * A problem whose qweight_list entry is NULL is skipped and its output left untouched (expert parallelism: the pairs routed to
+ * another rank's experts).
  * (No counterpart in the reference, which ships no MoE runtime kernel: docs/ADAPTERS.md:19.) */
 size_t htr_linear_grouped_workspace_bytes(int count, int m, int n, int K);
 int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* qweight_list, int mt, int nt, int K,

@@ -169,6 +169,16 @@ def _nccl_worker(rank, world, port, q):
             xi = (x * (i + 1)).contiguous()
             want = ops.linear(xi, qw.to(dev), sc.to(dev), su.to(dev), sv.to(dev))
             ok = ok and bool(torch.equal(peer(xi), want))
+        # expert-parallel MoE, 8 experts over the two ranks: device-routed grouped launches (pairs of the other rank's experts are
+        # skipped by the kernel) against host routing and against the CPU reference
+        from htr_b200.sharded import ExpertParallelMoE
+
+        experts, xm, ids, w = _moe_inputs(E=8, h=256, inter=128, T=6, k=2, K=3, seed=4)
+        moe = ExpertParallelMoE(experts, device=dev)
+        y_grp = moe(xm.to(dev), ids, w).float().cpu()
+        y_loop = moe(xm.to(dev), ids, w, grouped=False).float().cpu()
+        want = _moe_reference(experts, xm, ids, w, _oracle_linear())
+        ok = ok and float((y_grp - want).norm() / want.norm()) <= 1e-5 and float((y_loop - want).norm() / want.norm()) <= 1e-5
         torch.cuda.synchronize()
         q.put((rank, ok, tuple(y.shape)))
     finally:
