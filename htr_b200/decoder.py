@@ -9,8 +9,10 @@ projections (q|k|v, gate|up) are single packed linears, as the format prescribes
 Every packed linear goes through `htr_b200.ops.linear`.  The glue between them (residual add + RMSNorm, rotary embedding
 + KV-cache write, single-query grouped attention, SwiGLU) runs as four small fused kernels of the library
 (`htr_dec_*`, launched with programmatic stream serialisation so the following packed GEMV prefetches its weights while
-they run); `fused=False` evaluates the same glue with plain torch ops, which is how the kernels are checked.  A decode
-step reads its position from a device tensor, so one CUDA graph captured once serves every step.
+they run); `fused=False` evaluates the same glue with plain torch ops, which is how the kernels are checked.  Steps of at
+most 8 rows (decoding) fold the norms, the SwiGLU and the residual adds into the packed GEMVs themselves
+(`ops.linear_fused`) and, for a single token, the rotary embedding and cache write into the attention kernel: five launches
+per layer.  A decode step reads its position from a device tensor, so one CUDA graph captured once serves every step.
 """
 import dataclasses
 import math
