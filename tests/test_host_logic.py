@@ -50,6 +50,30 @@ def test_status_codes_without_touching_the_gpu(lib):
     assert L.htr_dequant_w(None, 8, 8, 4, None, None, None, None, 7, None) == -3
     assert b"K" in L.htr_status_string(-1)
     assert L.htr_linear_counter_bytes(4096) == 65536
+    # the later entry points validate their arguments the same way, before any CUDA call
+    import ctypes
+
+    f = ctypes.c_float(1e-6)
+    assert L.htr_linear_padded(None, 0, 1, 100, None, 8, 8, 4, None, None, None, None, None, 128, None, 0, None) == -2   # n_in % 8
+    assert L.htr_linear_padded(None, 0, 1, 136, None, 8, 8, 4, None, None, None, None, None, 128, None, 0, None) == -2   # n_in > n
+    assert L.htr_linear_padded(None, 0, 1, 128, None, 8, 8, 4, None, None, None, None, None, 132, None, 0, None) == -2   # m_out % 8, > m
+    assert L.htr_linear_padded(None, 0, 1, 120, None, 8, 8, 4, None, None, None, None, None, 72, None, 0, None) == -5    # NULL tensors
+    assert L.htr_linear_padded(None, 0, 0, 120, None, 8, 8, 4, None, None, None, None, None, 72, None, 0, None) == 0     # no rows
+    assert L.htr_linear_fused(None, 1, None, 8, 8, 4, None, None, None, None, None, 0, None, 3, None, f, 0) == -2        # unknown prologue
+    assert L.htr_linear_fused(None, 1, None, 8, 8, 4, None, None, None, None, None, 0, None, 1, None, f, 0) == -5        # norm weight missing
+    assert L.htr_linear_fused(None, 1, None, 8, 8, 4, None, None, None, None, None, 0, None, 0, None, f, 2) == -2        # residual flag
+    assert L.htr_linear_fused(None, 9, None, 8, 8, 4, None, None, None, None, None, 0, None, 0, None, f, 0) == -2        # more than 8 rows
+    assert L.htr_linear_gemm(None, 0, 257, None, 8, 8, 4, None, None, None, None, None, None, 0, None) == -2             # more than 256 rows
+    assert L.htr_linear_gemm(None, 0, 16, None, 8, 8, 7, None, None, None, None, None, None, 0, None) == -1
+    assert L.htr_linear_gemm(None, 0, 16, None, 8, 8, 4, None, None, None, None, None, None, 0, None) == -5
+    assert L.htr_linear_gemm(None, 0, 0, None, 8, 8, 4, None, None, None, None, None, None, 0, None) == 0
+    assert L.htr_viterbi(None, None, 4, 256, 7, 1, None, None, None, 0, None) == -1
+    assert L.htr_viterbi(None, None, 4, 300, 4, 1, None, None, None, 0, None) == -2                                       # more than 256 steps
+    assert L.htr_viterbi(None, None, 4, 256, 4, 1, None, None, None, 0, None) == -5
+    assert L.htr_viterbi(None, None, 0, 256, 4, 1, None, None, None, 0, None) == 0
+    assert L.htr_codebook_f32(None, None) == -5
+    assert L.htr_dec_rope_attention(None, None, None, None, None, None, None, 8, 2, 128, None) == -5
+    assert L.htr_linear_grouped(None, 0, None, 8, 8, 4, None, None, None, None, 0, None, 0, None) == 0                    # no problems
 
 
 def test_kernel_decode_arithmetic_on_the_host(tmp_path):
