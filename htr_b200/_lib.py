@@ -16,7 +16,7 @@ GEMM_MAX_ROWS_F32 = 128
 INPUT_INDEPENDENT = 1
 
 EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
-           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_peers", "htr_linear_grouped", "htr_linear_grouped_workspace_bytes", "htr_linear_static", "htr_linear_padded", "htr_linear_fused", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_linear_gemm_last_cuda_error", "htr_dequant_w", "htr_viterbi", "htr_viterbi_workspace_bytes", "htr_viterbi_last_cuda_error", "htr_codebook_f32",
+           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_peers", "htr_linear_grouped", "htr_linear_grouped_workspace_bytes", "htr_linear_routed", "htr_linear_static", "htr_linear_padded", "htr_linear_fused", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_linear_gemm_last_cuda_error", "htr_dequant_w", "htr_viterbi", "htr_viterbi_workspace_bytes", "htr_viterbi_last_cuda_error", "htr_codebook_f32",
            "htr_set_gemv_ctas_per_sm", "htr_linear_plan", "htr_dec_add_rmsnorm", "htr_dec_rope_cache", "htr_dec_attention",
            "htr_dec_swiglu", "htr_dec_rope_attention")
 
@@ -45,6 +45,7 @@ def _load():
     lib.htr_linear_ex.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp, ctypes.c_uint]
     lib.htr_linear_peers.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, vp, sz, vp, ctypes.c_uint]
     lib.htr_linear_grouped.argtypes = [vp, i32, vp, i32, i32, i32, vp, vp, vp, vp, i32, vp, sz, vp]
+    lib.htr_linear_routed.argtypes = [vp, i32, i32, i64, vp, i32, vp, vp, vp, vp, i32, i32, i32, vp, i32, vp, sz, vp]
     lib.htr_linear_grouped_workspace_bytes.restype = sz
     lib.htr_linear_grouped_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.htr_linear_static.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp]

@@ -130,6 +130,10 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
                          const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
                          int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags,
                          int prologue = 0, const void* norm_w = nullptr, float eps = 0.f, int residual = 0);
+static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
+                          const int64_t* route, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
+                          const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
+                          void* workspace, size_t workspace_bytes, htr_stream_t stream);
 
 
 const char* htr_status_string(int status) {
@@ -273,6 +277,10 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
   p.n_in = n_in;
   p.m_out = m_out;
+  p.g_route = nullptr;
+  p.g_xdiv = 1;
+  p.g_xrow_bytes = 0;
+  p.g_yrow_bytes = 0;
   p.prologue = prologue;
   p.residual = residual;
   p.x_stride = prologue == 2 ? 2 * n_in : n_in;
@@ -310,11 +318,34 @@ size_t htr_linear_grouped_workspace_bytes(int count, int m, int n, int K) {
 int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                        const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, void* const* y_list,
                        int count, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+  if (count > 0 && (!x_list || !y_list)) return HTR_ERR_NULL;
+  return launch_grouped(x_list, y_list, nullptr, nullptr, 1, 0, nullptr, 0, dtype, qweight_list, mt, nt, K, scales_list, su_list, sv_list, count,
+                        workspace, workspace_bytes, stream);
+}
+
+int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count,
+                      const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
+                      const uint8_t* const* sv_table, int mt, int nt, int K, void* y, int prologue, void* workspace, size_t workspace_bytes,
+                      htr_stream_t stream) {
+  if (count > 0 && (!x || !y || !route)) return HTR_ERR_NULL;
+  if (x_div < 1 || x_row_stride < 0 || (prologue != HTR_PROLOGUE_NONE && prologue != HTR_PROLOGUE_SWIGLU)) return HTR_ERR_BAD_SHAPE;
+  if (prologue == HTR_PROLOGUE_SWIGLU && dtype != HTR_DTYPE_BF16) return HTR_ERR_BAD_DTYPE;
+  if (count > 0 && (!aligned16(x) || !aligned16(y))) return HTR_ERR_ALIGNMENT;
+  return launch_grouped(nullptr, nullptr, x, y, x_div, x_row_stride, route, prologue, dtype, qweight_table, mt, nt, K, scales_table, su_table,
+                        sv_table, count, workspace, workspace_bytes, stream);
+}
+
+// shared body of the grouped entry points: per-problem pointer lists (x_list / y_list), or a route into per-expert tables with the
+// activations and outputs as rows of two matrices
+static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
+                          const int64_t* route, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
+                          const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
+                          void* workspace, size_t workspace_bytes, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (count < 0 || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
   if (count == 0) return HTR_OK;
-  if (!x_list || !qweight_list || !scales_list || !su_list || !sv_list || !y_list) return HTR_ERR_NULL;
+  if (!qweight_list || !scales_list || !su_list || !sv_list) return HTR_ERR_NULL;
   const int m = mt * 16, n = nt * 16, rbp = m / 128;
   if ((long long)count * rbp > kCounterBytes / 4) return HTR_ERR_TOO_LARGE;
   if (!aligned16(workspace)) return HTR_ERR_ALIGNMENT;
@@ -334,7 +365,7 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
 
   GemvParams p;
-  p.x = nullptr; p.qw = nullptr; p.scales = nullptr; p.su = nullptr; p.sv = nullptr; p.bias = nullptr; p.y = nullptr;
+  p.x = x; p.qw = nullptr; p.scales = nullptr; p.su = nullptr; p.sv = nullptr; p.bias = nullptr; p.y = y;
   p.counters = static_cast<int*>(workspace);
   p.part = reinterpret_cast<float*>(static_cast<char*>(workspace) + counter_bytes(m));
   p.rows = 1;
@@ -350,11 +381,16 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
   p.npeer = 0;
   p.n_in = nt * 16;
   p.m_out = mt * 16;
-  p.prologue = 0;
+  p.prologue = prologue;
   p.residual = 0;
-  p.x_stride = nt * 16;
+  p.x_stride = prologue == HTR_PROLOGUE_SWIGLU ? 2 * nt * 16 : nt * 16;
   p.norm_w = nullptr;
   p.eps = 0.f;
+  p.g_route = reinterpret_cast<const long long*>(route);
+  p.g_xdiv = x_div;
+  const long long esz = dtype == HTR_DTYPE_F32 ? 4 : 2;
+  p.g_xrow_bytes = (long long)x_row_stride * esz;
+  p.g_yrow_bytes = (long long)m * esz;
   p.peer_offset = 0;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
   p.group = count;

@@ -98,7 +98,12 @@ struct GemvParams {
   const __half* const* g_scales;
   const uint8_t* const* g_su;
   const uint8_t* const* g_sv;
-  void* const* g_y;         // 1 / rms of the codebook integers
+  void* const* g_y;
+  // Routed form: g_route[prob] = index into the four tables above (e.g. the expert of a (token, slot) pair); activations are
+  // row prob / g_xdiv of the matrix at x (g_xrow_bytes apart), outputs row prob of the matrix at y (g_yrow_bytes apart).
+  const long long* g_route;
+  int g_xdiv;
+  long long g_xrow_bytes, g_yrow_bytes;         // 1 / rms of the codebook integers
 };
 
 // four consecutive activations of row r at column col (a multiple of 4); columns at or beyond n_in (a multiple of 4) read as zero
@@ -272,13 +277,19 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     asm volatile("griddepcontrol.wait;" ::: "memory");            // the pointer lists may come from the preceding kernel
     const int prob = rb / p.rb_per_problem;
     rb_base = prob * p.rb_per_problem;
-    x_ptr = p.g_x[prob];
-    qw_ptr = p.g_qw[prob];
+    const long long entry = p.g_route ? p.g_route[prob] : prob;      // which row of the pointer tables
+    qw_ptr = p.g_qw[entry];
     if (qw_ptr == nullptr) return;                                  // a problem this rank does not own (expert parallelism): nothing to do
-    scales_ptr = p.g_scales[prob];
-    su_ptr = p.g_su[prob];
-    sv_ptr = p.g_sv[prob];
-    y_ptr = p.g_y[prob];
+    scales_ptr = p.g_scales[entry];
+    su_ptr = p.g_su[entry];
+    sv_ptr = p.g_sv[entry];
+    if (p.g_route) {
+      x_ptr = static_cast<const char*>(p.x) + (size_t)(prob / p.g_xdiv) * p.g_xrow_bytes;
+      y_ptr = static_cast<char*>(p.y) + (size_t)prob * p.g_yrow_bytes;
+    } else {
+      x_ptr = p.g_x[prob];
+      y_ptr = p.g_y[prob];
+    }
   }
 
   // prefetch cursor: runs kRing units ahead of the consumer along the same unit sequence.  Offsets are kept in

@@ -233,6 +233,29 @@ def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K
     _lib.check(rc, "htr_linear_grouped")
 
 
+def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, out=None):
+    """One launch over `route.numel()` problems (htr_linear_routed): problem i multiplies activation row i // x_div of `x` by the
+    packed matrix whose four tensor addresses sit in row route[i] of `tables` (four int64 CUDA tensors, one row per expert; a
+    zero weight address skips the problem) and writes row i of the result [count, m].  With prologue=PROLOGUE_SWIGLU the rows of
+    x are [gate | up] of 2n bf16 values.  Nothing touches the host: the routing result stays on the device."""
+    count = route.numel()
+    dev = x.device
+    if route.dtype != torch.int64 or not route.is_cuda or not x.is_contiguous() or x.dim() != 2:
+        raise _lib.HTRError("htr_linear_routed: route must be an int64 CUDA tensor and x a contiguous matrix")
+    if out is None:
+        out = torch.empty((count, mt * 16), dtype=x.dtype, device=dev)
+    need = _lib.lib.htr_linear_grouped_workspace_bytes(max(count, 1), mt * 16, nt * 16, K)
+    if need == 0:
+        raise _lib.HTRError("htr_linear_routed: unsupported sizes")
+    with torch.cuda.device(dev):
+        ws = workspace(dev, need)
+        rc = _lib.lib.htr_linear_routed(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count, tables[0].data_ptr(),
+                                        tables[1].data_ptr(), tables[2].data_ptr(), tables[3].data_ptr(), mt, nt, K, out.data_ptr(), int(prologue),
+                                        ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(rc, "htr_linear_routed")
+    return out
+
+
 class independent_inputs:
     """Context manager: inside it, every packed linear promises that its activations, bias and output are not
     touched by the kernel launched just before it on the stream (e.g. the experts of one MoE layer, or the

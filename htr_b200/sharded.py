@@ -202,36 +202,33 @@ class ExpertParallelMoE:
         return self._tables
 
     def partial_grouped(self, x, topk_ids, topk_w):
-        """The same contribution with two grouped launches (gate_up, down) over all (token, slot) pairs.  Routing stays on
-        the device (no host round trip, capturable in a CUDA graph); pairs routed to another rank's experts are skipped by
-        the kernel (null weight pointer) and contribute zero here."""
+        """The same contribution with two routed launches over all (token, slot) pairs: gate_up reads token row pair // k, down
+        reads the pair's [gate | up] row and applies SwiGLU while staging it (bf16; other dtypes use a separate activation step).
+        Routing stays on the device (no host round trip, capturable in a CUDA graph); pairs routed to another rank's experts are
+        skipped by the kernel (null weight address) and contribute zero here."""
         from . import ops
 
         T, hdim = x.shape
         k = topk_ids.shape[1]
-        P = T * k
         dev = x.device
         tabs = self._address_tables(dev)
-        e_idx = topk_ids.to(dev).reshape(-1).to(torch.int64)
-        gq, gs, gu_, gv = (t.index_select(0, e_idx) for t in tabs["gate_up"])
-        dq, ds, du, dv = (t.index_select(0, e_idx) for t in tabs["down"])
+        route = topk_ids.to(device=dev, dtype=torch.int64).reshape(-1).contiguous()
         any_e = next(iter(self.local.values()))
         mt_gu, nt_gu, W = any_e["gate_up"][0].shape
         mt_dn, nt_dn, _ = any_e["down"][0].shape
         K = W // 8
-        esz = x.element_size()
         x = x.contiguous()
-        tok = torch.arange(T, device=dev, dtype=torch.int64).repeat_interleave(k)
-        gu = torch.zeros(P, mt_gu * 16, dtype=x.dtype, device=dev)       # rows of skipped pairs stay zero
-        slot = torch.arange(P, device=dev, dtype=torch.int64)
-        ops.linear_grouped(x.data_ptr() + tok * (hdim * esz), gq, gs, gu_, gv, gu.data_ptr() + slot * (mt_gu * 16 * esz),
-                           mt_gu, nt_gu, K, x.dtype)
-        inter = mt_gu * 8
-        act = torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]
-        dn = torch.zeros(P, mt_dn * 16, dtype=x.dtype, device=dev)
-        ops.linear_grouped(act.data_ptr() + slot * (inter * esz), dq, ds, du, dv, dn.data_ptr() + slot * (mt_dn * 16 * esz),
-                           mt_dn, nt_dn, K, x.dtype)
-        return (dn.view(T, k, -1).float() * topk_w.to(device=dev, dtype=torch.float32)[:, :, None]).sum(1)
+        skip = self.world > 1                                            # rows of skipped pairs must read as zero
+        alloc = torch.zeros if skip else torch.empty
+        gu = ops.linear_routed(x, route, tabs["gate_up"], mt_gu, nt_gu, K, x_div=k, out=alloc(T * k, mt_gu * 16, dtype=x.dtype, device=dev))
+        dn = alloc(T * k, mt_dn * 16, dtype=x.dtype, device=dev)
+        if x.dtype == torch.bfloat16:
+            ops.linear_routed(gu, route, tabs["down"], mt_dn, nt_dn, K, prologue=ops.PROLOGUE_SWIGLU, out=dn)
+        else:
+            inter = mt_gu * 8
+            act = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).contiguous()
+            ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, out=dn)
+        return torch.einsum("tkh,tk->th", dn.view(T, k, -1).float(), topk_w.to(device=dev, dtype=torch.float32))
 
     def partial(self, x, topk_ids, topk_w):
         """Contribution of this rank's experts, float32 [T, h].  Routing is resolved on the host."""

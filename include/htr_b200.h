@@ -117,6 +117,21 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
 int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
                       const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, htr_stream_t stream);
 
+#define HTR_PROLOGUE_NONE 0
+#define HTR_PROLOGUE_RMSNORM 1
+#define HTR_PROLOGUE_SWIGLU 2
+
+/* Routed form of the grouped launch: problem i uses row route[i] of four DEVICE tables of device pointers (one row per expert;
+ * a NULL qweight entry skips the problem), reads activation row i / x_div of the matrix at x (rows x_row_stride elements apart)
+ * and writes row i of y[count][m].  With x_div = top-k and route = the router's expert ids this is the gate_up launch of a
+ * mixture-of-experts step with no pointer arithmetic on the host or in framework kernels; the down launch uses x_div = 1 and
+ * prologue = HTR_PROLOGUE_SWIGLU, in which x holds [gate | up] rows of 2n bf16 values and the linear sees
+ * silu(gate) * up.  Workspace as for htr_linear_grouped. */
+int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count,
+                      const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
+                      const uint8_t* const* sv_table, int mt, int nt, int K, void* y, int prologue, void* workspace,
+                      size_t workspace_bytes, htr_stream_t stream);
+
 /* Padded form (the reference's HTRHCLinearMethod.apply, htr/vllm_plugin.py:313-326: F.pad of the input to n_pad, slice of
  * the output to m_out, both as separate copies there): the stored tensors cover a padded [m = 16*mt, n = 16*nt] matrix, x has
  * only n_in <= n columns per row (row stride n_in; the missing columns count as zeros) and y receives only the first
@@ -132,9 +147,6 @@ int htr_linear_padded(const void* x, int dtype, int M, int n_in, const void* qwe
  *   prologue HTR_PROLOGUE_SWIGLU  : x holds [gate | up] rows of 2n values; the linear's input is silu(gate) * up
  *   residual 1                    : y[M][m] is the residual stream, y <- y + result (in place) instead of y <- result
  * Intermediate values are rounded to bf16 exactly where the unfused bf16 operators round them. */
-#define HTR_PROLOGUE_NONE 0
-#define HTR_PROLOGUE_RMSNORM 1
-#define HTR_PROLOGUE_SWIGLU 2
 int htr_linear_fused(const void* x, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
                      const uint8_t* sv, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream, int prologue,
                      const void* norm_weight, float eps, int residual);

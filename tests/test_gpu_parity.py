@@ -228,3 +228,32 @@ def test_workspace_counters_stay_zero(dev):
     for buf in ops._WORKSPACES.values():
         nb = _lib.lib.htr_linear_counter_bytes(512 * 64)
         assert int(buf[:nb].to(torch.int64).sum()) == 0
+
+
+@pytest.mark.parametrize("K", (2, 3, 4, 5))
+def test_routed_launch_equals_one_call_per_problem(dev, K):
+    """htr_linear_routed: device-side route into per-expert pointer tables, shared activation rows, a skipped (null) expert,
+    and the SwiGLU prologue -- each problem bit-identical to its own htr_linear call."""
+    from htr_b200 import ops
+
+    E, m, n, T, k = 5, 256, 384, 3, 2
+    experts = [packed(m, n, K, 70 + e, dev) for e in range(E)]
+    tables = [torch.tensor([experts[e][i].data_ptr() if e != 3 else 0 for e in range(E)], dtype=torch.int64, device=dev) for i in range(4)]
+    route = torch.tensor([0, 4, 2, 2, 3, 1], dtype=torch.int64, device=dev)          # pair (token 2, slot 0) hits the absent expert
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(T, n, device=dev).to(dtype)
+        out = torch.full((T * k, m), 7.0, dtype=dtype, device=dev)
+        got = ops.linear_routed(x, route, tables, m // 16, n // 16, K, x_div=k, out=out)
+        assert got is out
+        for i, e in enumerate(route.tolist()):
+            if e == 3:
+                assert bool((out[i] == 7.0).all())                                     # untouched
+            else:
+                assert torch.equal(out[i:i + 1], ops.linear(x[i // k:i // k + 1], *experts[e]))
+    # down-projection form: rows of [gate | up], SwiGLU applied while staging
+    gu = torch.randn(T * k, 2 * n, device=dev).bfloat16()
+    got = ops.linear_routed(gu, route, tables, m // 16, n // 16, K, prologue=ops.PROLOGUE_SWIGLU)
+    for i, e in enumerate(route.tolist()):
+        if e != 3:
+            want = ops.linear_fused(gu[i:i + 1].contiguous(), *experts[e], prologue=ops.PROLOGUE_SWIGLU)
+            assert torch.equal(got[i:i + 1], want)
