@@ -82,7 +82,7 @@ struct GemvParams {
   int x_stride;     // elements between activation rows (n_in; 2n for prologue 2)
   const void* norm_w;
   float eps;
-  float cb;
+  float cb;         // 1 / rms of the codebook integers
   // Peer form (row-sharded linears over NVLink): when npeer > 0 the epilogue writes its rows into every listed buffer
   // (peers' and its own, plain stores through peer-mapped addresses) at element offset peer_offset, instead of into y.
   void* peer_y[8];
@@ -103,7 +103,7 @@ struct GemvParams {
   // row prob / g_xdiv of the matrix at x (g_xrow_bytes apart), outputs row prob of the matrix at y (g_yrow_bytes apart).
   const long long* g_route;
   int g_xdiv;
-  long long g_xrow_bytes, g_yrow_bytes;         // 1 / rms of the codebook integers
+  long long g_xrow_bytes, g_yrow_bytes;
 };
 
 // four consecutive activations of row r at column col (a multiple of 4); columns at or beyond n_in (a multiple of 4) read as zero
