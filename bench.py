@@ -381,13 +381,14 @@ def run_ours(args):
                     e2e={"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
                     roofline={"bound": "hbm", "kernel": "packed_gemv_kernel<K,1>", "achieved": achieved, "peak": peak, "unit": "GB/s",
                               "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
-                              "traffic_note": "ncu dram__bytes_read+write on the 151936x4096 K4 launch: 318.2 MB for 311.5 MB "
-                                              "algorithmic (profiles/); 1.02x, proportional to packed bytes",
+                              "traffic_note": "ncu dram__bytes_read+write on one 4096x12288 K4 launch of this workload: 25.25 MB for "
+                                              "25.19 MB algorithmic (profiles/packed_gemv_K4_mlp_4096x12288_M1.md); 1.002x, "
+                                              "proportional to packed bytes for the other widths",
                               "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / launches,
                               "per_K": per_k},
                     stream_ordered=overlapped,
                     timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs and not graph_note else "eager launches " + "; ".join(graph_note)))
-        line["roofline"]["traffic"] = round(1.0215 * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
+        line["roofline"]["traffic"] = round(1.0024 * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, sample = cpu_sample()
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
