@@ -45,6 +45,9 @@ def test_search_matches_the_oracle_on_fresh_tiles(coracle, K):
     x[3] *= 3.0                                                         # a tile mostly outside the codebook's range
     w[5] = 1.0                                                          # unit weights: many exactly equal costs, ties matter
     x[5] = torch.round(x[5] * 4) / 4
+    x[7] = 0.0                                                          # degenerate tiles: all-zero targets,
+    x[8] = x[8, :1]                                                     # a constant target (every step ties),
+    w[9, ::2] = 1e-6                                                    # weights spanning six orders of magnitude
     want, want_cost = coracle.viterbi(x.numpy(), w.numpy(), K)
     cb = torch.from_numpy(wire.codebook_f32()).to(dev)                  # the hook's third argument, as the reference passes it
     got, cost = encoder.viterbi(x.to(dev), w.to(dev), cb, K, return_cost=True)
