@@ -145,7 +145,7 @@ def base_line(args, impl=None):
     d = {"metric": "packed_gemv_weight_GBps_batch1", "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
          "config": {"workload": "mlp_bitrate_sweep_batch1", "shapes_m_x_n": [list(s) for s in SHAPES], "K": list(WIDTHS), "batch": 1,
-                    "copies_per_shape_and_K": COPIES, "activations": "bf16 N(0,1)",
+                    "copies_per_shape_and_K": COPIES, "activations": "bf16 N(0,1)", "weights": "encoder output" if args.real_streams else "uniform random words",
                     "launch_form": "independent linears: htr_linear_ex(HTR_LINEAR_INPUT_INDEPENDENT), consecutive launches overlap; "
                                    "stream_ordered gives the default form",
                     "l2_policy": "inputs larger than L2: every K-group of a pass holds >= 201 MB of distinct packed weights",
@@ -210,6 +210,29 @@ def run_ours(args):
                 total_bytes += payload_bytes(m, n, K)
                 launches += 1
         groups.append(items)
+    if args.real_streams:
+        # replace the uniform random words by real encoder output: one synthetic weight per (K, shape), Hessian from activations with
+        # 1 % outlier channels, encoded on this GPU (htr_b200.encoder), copied into every buffer of that (K, shape)
+        from htr_b200 import encoder
+        t_enc = time.time()
+        for K, items in zip(WIDTHS, groups):
+            done = {}
+            for it in items:
+                key = (it["m"], it["n"])
+                if key not in done:
+                    ge = torch.Generator().manual_seed(77 + K + it["m"])
+                    W = (torch.randn(it["m"], it["n"], generator=ge) * 0.02).to(dev)
+                    X = torch.randn(512, it["n"], generator=ge)
+                    X[:, torch.randperm(it["n"], generator=ge)[: it["n"] // 100]] *= 10.0
+                    X = X.to(dev)
+                    r = encoder.encode_group([{"W": W, "H": X.T @ X / 512}], K, seed=1234)[0]
+                    done[key] = (r["qweight"], r["scales"], r["su"], r["sv"])
+                    del W, X, r
+                for dst, src in zip(it["w"], done[key]):
+                    dst.copy_(src)
+            torch.cuda.empty_cache()
+        if rank == 0:
+            print(f"# encoded {len(WIDTHS) * len(SHAPES)} matrices in {time.time() - t_enc:.1f} s", file=sys.stderr, flush=True)
     # end-to-end form: the activations of a K-group travel in one host->device copy (pinned pool), its outputs in one
     # device->host copy; the items hold views of the pools
     for items in groups:
@@ -573,6 +596,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--workload", default="mlp", choices=("mlp", "lmhead", "decoder", "moe", "viterbi"),
                     help="mlp = the default benchmark line; the others print lines for the remaining configurations")
+    ap.add_argument("--real-streams", action="store_true",
+                    help="mlp workload: packed words from the device-side encoder (real tail-biting streams) instead of uniform random words")
     ap.add_argument("--case", default=None, help="run one small fixed case for a profiler and exit, e.g. K=4,m=4096,n=12288,M=64")
     args = ap.parse_args()
     if args.case:
