@@ -87,6 +87,8 @@ struct GemmParams {
   int dtype;
   int hb;                 // 128-column blocks per row (n / 128) = units per row block
   int split;              // CTAs per row block
+  int cluster;            // 1: the CTAs of a row block were launched as one thread-block cluster (split <= 8): the split reduction
+                          // goes through distributed shared memory instead of global partial sums
   int stages;             // stage pairs in the ring (2..kMaxStages)
   int xsum_slices;
   float cb;
@@ -442,6 +444,42 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
   __syncthreads();
   HTR_GTRACE(tid == 0, 3);
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+
+  if (p.cluster) {
+    // ---- split reduction inside the cluster: every CTA keeps its partial [np][128] where it is; CTA r of the cluster sums rows
+    // r, r + split, ... over all CTAs (in rank order: the same additions as the global path) and finishes those rows itself
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const int row0 = rb * 128 + 4 * lane;
+    const uint2 sc_raw = __ldg(reinterpret_cast<const uint2*>(p.scales + row0));
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.y));
+    const unsigned sv_bits = sign_nibble(p.sv, rb * 32 + lane);
+    float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
+    const uint32_t result_addr = smem_u32(result);
+    for (int j = part_id + p.split * warp; j < p.rows; j += p.split * kGemmWarps) {
+      float4 r4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < p.split; ++r) {
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(result_addr + (uint32_t)(j * 128 + 4 * lane) * 4u), "r"(r));
+        float4 v;
+        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(remote) : "memory");
+        r4.x += v.x; r4.y += v.y; r4.z += v.z; r4.w += v.w;
+      }
+      float xs = 0.f;
+      for (int y = 0; y < p.xsum_slices; ++y) xs += p.xsum[j * p.xsum_slices + y];
+      const float off = 1534.0f * xs, rs = p.cb * p.tok[j];
+      float v[4] = {(r4.x - off) * (s01.x * rs), (r4.y - off) * (s01.y * rs), (r4.z - off) * (s23.x * rs), (r4.w - off) * (s23.y * rs)};
+      wht128(v, lane);
+      float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
+                             flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
+      o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
+      store_quad(p.y, (size_t)j * m + row0, p.dtype, o);
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // nobody leaves while its shared memory may still be read
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    return;
+  }
 
   // ---- split reduction across the CTAs of this row block (same scheme as the GEMV), then the epilogue
   bool finish = true;

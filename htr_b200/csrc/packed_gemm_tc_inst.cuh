@@ -15,12 +15,42 @@ int launch_packed_gemm_tc<HTR_INST_K>(const GemmParams& p, int grid, cudaStream_
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (int)cudaLaunchKernelEx(&cfg, packed_gemm_tc_kernel<HTR_INST_K>, p);
+  GemmParams q = p;
+  q.cluster = 0;
+#ifndef HTR_GEMM_NO_CLUSTER
+  if (p.split >= 2 && p.split <= 8) {
+    // the CTAs of a row block as one cluster, when every cluster of the grid can be resident at once
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = (unsigned)p.split;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.numAttrs = 2;
+    // the occupancy query costs tens of microseconds on the host: remember the answer per (device, cluster size, shared memory)
+    struct Seen { int dev, split, smem, clusters; };
+    static thread_local Seen seen[8] = {};
+    static thread_local int next_slot = 0;
+    int dev = 0, clusters = -1;
+    cudaGetDevice(&dev);
+    for (const Seen& c : seen)
+      if (c.split == p.split && c.smem == smem && c.dev == dev) clusters = c.clusters;
+    if (clusters < 0) {
+      if (cudaOccupancyMaxActiveClusters(&clusters, packed_gemm_tc_kernel<HTR_INST_K>, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        clusters = 0;
+      }
+      seen[next_slot] = Seen{dev, p.split, smem, clusters};
+      next_slot = (next_slot + 1) % 8;
+    }
+    if (clusters * p.split >= grid) q.cluster = 1;
+    else cfg.numAttrs = 1;
+  }
+#endif
+  return (int)cudaLaunchKernelEx(&cfg, packed_gemm_tc_kernel<HTR_INST_K>, q);
 }
 
 }  // namespace htr
