@@ -3,13 +3,17 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "packed_gemv.cuh"
+#include "packed_gemv_tc.cuh"
 
 namespace htr {
 int run_decode_raw(int K, const uint32_t* qw, int16_t* out, long long ntiles, cudaStream_t st);
 int run_rht(const void* x, int dtype, int M, int n, const uint8_t* su, float* xt, cudaStream_t st);
 int run_dequant_w(int K, const uint32_t* qw, const __half* scales, const uint8_t* su, const uint8_t* sv, float cb, void* W,
                   int out_dtype, int mt, int nt, cudaStream_t st);
+
+#ifndef HTR_GEMV_TC_DEFAULT
+#define HTR_GEMV_TC_DEFAULT 0
+#endif
 
 static thread_local int t_last_cuda = 0;
 static int g_ctas_override = 0;
@@ -49,6 +53,27 @@ static int gemv_ctas_per_sm(int K, int mt_rows) {
   return -1;
 }
 
+static int gemv_tc_ctas_per_sm(int K) {
+  switch (K) {
+    case 2: return packed_gemv_tc_ctas_per_sm<2>();
+    case 3: return packed_gemv_tc_ctas_per_sm<3>();
+    case 4: return packed_gemv_tc_ctas_per_sm<4>();
+    case 5: return packed_gemv_tc_ctas_per_sm<5>();
+    case 6: return packed_gemv_tc_ctas_per_sm<6>();
+    case 8: return packed_gemv_tc_ctas_per_sm<8>();
+  }
+  return -1;
+}
+
+// HTR_GEMV_TC=0 in the environment keeps every batch size on the CUDA-core GEMV (for A/B timing and as a fallback switch)
+static bool gemv_tc_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("HTR_GEMV_TC");
+    return v ? v[0] != '0' : HTR_GEMV_TC_DEFAULT != 0;
+  }();
+  return on;
+}
+
 bool gemv_overlap_enabled() {
   static const bool on = [] {
     const char* v = std::getenv("HTR_GEMV_OVERLAP");
@@ -83,7 +108,21 @@ static int cached_occupancy(int dev, int K, int rows_t) {
   return slot;
 }
 
-static int make_plan(int M, int m, int n, int K, Plan* out) {
+static int cached_tc_occupancy(int dev, int K) {
+  static int cache[64][9] = {{0}};
+  static std::mutex mu;
+  if (dev < 0 || dev >= 64) return gemv_tc_ctas_per_sm(K);
+  std::lock_guard<std::mutex> lock(mu);
+  int& slot = cache[dev][K];
+  if (slot == 0) slot = gemv_tc_ctas_per_sm(K);
+  return slot;
+}
+
+// the tensor-core GEMV serves single problems of up to four activation rows
+static int g_tc_override = -1;                         // -1: environment / build default, 0: off, 1: on
+static bool use_tc(int M) { return (g_tc_override >= 0 ? g_tc_override != 0 : gemv_tc_enabled()) && M <= kTcRows; }
+
+static int make_plan(int M, int m, int n, int K, Plan* out, bool tc = false) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail((int)e);
@@ -91,7 +130,7 @@ static int make_plan(int M, int m, int n, int K, Plan* out) {
   if (sms <= 0) return cuda_fail((int)cudaErrorInvalidDevice);
   Plan pl;
   pl.rows_t = template_rows(M);
-  int per_sm = g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
+  int per_sm = tc ? cached_tc_occupancy(dev, K) : g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
   if (per_sm <= 0) return cuda_fail((int)cudaErrorLaunchOutOfResources);
   pl.rbs = m / 128;
   pl.cg = n / 64;
@@ -155,6 +194,7 @@ int htr_last_cuda_error(void) { return t_last_cuda; }
 int htr_version(void) { return 100; }
 
 void htr_set_gemv_ctas_per_sm(int ctas) { g_ctas_override = ctas > 0 ? ctas : 0; }
+void htr_set_gemv_tc(int mode) { g_tc_override = mode < 0 ? -1 : mode != 0; }
 
 int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
@@ -182,14 +222,20 @@ size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
   if (!width_ok(K) || M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return 0;
   Plan pl;
   if (make_plan(M, m, n, K, &pl) != HTR_OK) return 0;
-  return counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
+  size_t slots = (size_t)pl.slots;
+  if (use_tc(M)) {                                     // either kernel may serve the call: size for both
+    Plan tc;
+    if (make_plan(M, m, n, K, &tc, true) != HTR_OK) return 0;
+    if ((size_t)tc.slots > slots) slots = (size_t)tc.slots;
+  }
+  return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * sizeof(float);
 }
 
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return HTR_ERR_BAD_SHAPE;
   Plan pl;
-  const int rc = make_plan(M, m, n, K, &pl);
+  const int rc = make_plan(M, m, n, K, &pl, use_tc(M));
   if (rc != HTR_OK) return rc;
   if (grid) *grid = pl.grid;
   if (slots_per_block) *slots_per_block = pl.slots;
@@ -252,7 +298,8 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
     return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
   Plan pl;
-  const int rc = make_plan(M, m, n, K, &pl);
+  const bool tc = use_tc(M);
+  const int rc = make_plan(M, m, n, K, &pl, tc);
   if (rc != HTR_OK) return rc;
   const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
@@ -296,6 +343,17 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int e = 0;
+  if (tc) {
+    switch (K) {
+      case 2: e = launch_packed_gemv_tc<2>(p, pl.grid, st); break;
+      case 3: e = launch_packed_gemv_tc<3>(p, pl.grid, st); break;
+      case 4: e = launch_packed_gemv_tc<4>(p, pl.grid, st); break;
+      case 5: e = launch_packed_gemv_tc<5>(p, pl.grid, st); break;
+      case 6: e = launch_packed_gemv_tc<6>(p, pl.grid, st); break;
+      case 8: e = launch_packed_gemv_tc<8>(p, pl.grid, st); break;
+    }
+    return e ? cuda_fail(e) : HTR_OK;
+  }
   switch (K) {
     case 2: e = launch_packed_gemv<2>(p, pl.rows_t, pl.grid, st); break;
     case 3: e = launch_packed_gemv<3>(p, pl.rows_t, pl.grid, st); break;
@@ -305,6 +363,25 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
     case 8: e = launch_packed_gemv<8>(p, pl.rows_t, pl.grid, st); break;
   }
   return e ? cuda_fail(e) : HTR_OK;
+}
+
+int htr_gemv_tc_failures(int* count) {
+  if (!count) return HTR_ERR_NULL;
+  int total = 0, one = 0, e = 0;
+  if ((e = packed_gemv_tc_failures<2>(&one))) return cuda_fail(e);
+  total += one;
+  if ((e = packed_gemv_tc_failures<3>(&one))) return cuda_fail(e);
+  total += one;
+  if ((e = packed_gemv_tc_failures<4>(&one))) return cuda_fail(e);
+  total += one;
+  if ((e = packed_gemv_tc_failures<5>(&one))) return cuda_fail(e);
+  total += one;
+  if ((e = packed_gemv_tc_failures<6>(&one))) return cuda_fail(e);
+  total += one;
+  if ((e = packed_gemv_tc_failures<8>(&one))) return cuda_fail(e);
+  total += one;
+  *count = total;
+  return HTR_OK;
 }
 
 size_t htr_linear_grouped_workspace_bytes(int count, int m, int n, int K) {
