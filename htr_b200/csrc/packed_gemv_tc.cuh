@@ -36,22 +36,25 @@
 namespace htr {
 
 constexpr int kTcDecodeWarps = 8;
-constexpr int kTcWarps = kTcDecodeWarps + 1;
-constexpr int kTcThreads = kTcWarps * 32;                 // 288
 constexpr int kTcSlots = 2;                                // decode warp groups taking alternate units
-constexpr int kTcStages = 3;                               // A stages in TMEM
+constexpr int kTcLanes = 2 * kTcSlots;                     // MMA lanes: two per slot, each issues half of a unit's MMAs
+constexpr int kTcWarps = kTcDecodeWarps + kTcLanes;
+constexpr int kTcThreads = kTcWarps * 32;                 // 384: 3 warps per scheduler, two CTAs per SM at <= 80 registers
+constexpr int kTcStages = 3;                               // A stages in TMEM, used in turn by the units of a CTA
 constexpr int kTcStageCols = 64;                           // one unit: 64 weights per row
-constexpr int kTcAcol0 = 64;                               // first A column (accumulators: columns 0..15)
+constexpr int kTcAcol0 = 64;                               // first A column (accumulators: 16 columns per MMA lane in columns 0..63)
 constexpr int kTcTmemCols = 256;
-constexpr int kTcBlocks = 6;                               // 128-column blocks of activations per window
-constexpr int kTcWinUnits = 2 * kTcBlocks;
-constexpr int kTcUnitBBytes = 16 * 2 * 128;                // B operand of one unit: 16 k-groups x 2 n-groups x (8 x 16 bytes)
+constexpr int kTcWinBytes = 48 * 1024;                     // B operand of one window of activations
 constexpr int kTcRows = 4;                                 // activation rows per launch (x 4 planes = 16 accumulator columns)
+// B operand of one unit: 16 k-groups x n-groups x (8 x 16 bytes).  With one or two activation rows only the first n-group
+// (8 accumulator columns) carries data: it is stored alone and the descriptor repeats it for the second one (stride 0), whose
+// accumulator columns nobody reads.  So a window holds 24 units (1536 columns) for up to two rows and 12 units for three or four.
+__host__ __device__ constexpr int tc_unit_b_bytes(int rows) { return rows <= 2 ? 16 * 128 : 16 * 2 * 128; }
 
 __host__ __device__ constexpr int tc_ring_slots(int K) { return K <= 3 ? 6 : K == 4 ? 5 : K <= 6 ? 4 : 3; }
 __host__ __device__ constexpr int tc_slot_bytes(int K) { return 2 * 4 * 32 * K; }   // two strips x four tiles
 __host__ __device__ constexpr int gemv_tc_smem_bytes(int K) {
-  return kTcWinUnits * kTcUnitBBytes + kTcDecodeWarps * tc_ring_slots(K) * tc_slot_bytes(K) + 128 + 64;
+  return kTcWinBytes + kTcDecodeWarps * tc_ring_slots(K) * tc_slot_bytes(K) + 128 + 64;
 }
 
 __device__ __forceinline__ uint64_t umma_desc_kn(uint32_t smem_addr, int lbo_bytes, int sbo_bytes) {
@@ -83,6 +86,21 @@ __device__ __forceinline__ void tmem_load16_s32(uint32_t taddr, int (&v)[16]) {
       : "r"(taddr)
       : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// bounded wait with an explicit suspend-time hint (nanoseconds the hardware may park the thread before it looks again)
+__device__ __forceinline__ bool mbar_wait_hint(uint32_t bar, uint32_t parity, const volatile int* fail, uint32_t hint_ns) {
+  for (unsigned it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    if (done) return true;
+    if ((it & 255u) == 255u && *fail) return false;
+  }
+  return false;
 }
 
 namespace detail {
@@ -148,10 +166,25 @@ __device__ __forceinline__ void read_row_words(const uint32_t* __restrict__ tile
 // failures (expired waits) since the library was loaded, over all launches of this kernel on this device
 static __device__ int htr_gemv_tc_failures_dev = 0;
 
+#ifdef HTR_GEMV_TC_TRACE
+// timeline probe for experiments: per-CTA %globaltimer stamps, compiled only on request
+static __device__ unsigned long long htr_tc_trace_buf[512 * 160];
+__device__ __forceinline__ void tc_stamp(int slot) {
+  if (blockIdx.x < 512 && slot < 160) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    htr_tc_trace_buf[blockIdx.x * 160 + slot] = t;
+  }
+}
+#define HTR_TTRACE(cond, slot) do { if (cond) tc_stamp(slot); } while (0)
+#else
+#define HTR_TTRACE(cond, slot)
+#endif
+
 template <int K>
 __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char tsm[];
-  __shared__ __align__(8) unsigned long long s_afull[kTcStages], s_freed[kTcStages], s_done;
+  __shared__ __align__(8) unsigned long long s_afull[kTcStages], s_freed[kTcStages], s_done[kTcLanes];
   __shared__ uint32_t s_tmem;
   __shared__ int s_arrival;
   __shared__ volatile int s_fail;
@@ -163,6 +196,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qd = warp & 3, cs = warp >> 2;           // decode warps only
+  HTR_TTRACE(tid == 0, 0);
   const int U = p.units, G = gridDim.x, CG = p.cg, nt = p.nt, n = nt * 16, m = p.mt * 16;
   int u_begin, u_end;
   if (p.split > 0) {
@@ -177,26 +211,29 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
   constexpr int kTileBytes = 32 * K, kSlotBytes = tc_slot_bytes(K), R = tc_ring_slots(K), kSlotChunks = kSlotBytes / 16;
 
   unsigned char* bwin = tsm + (128 - (smem_u32(tsm) & 127)) % 128;              // B operand of the window, [unit][k-group][n-group][8][16]
-  unsigned char* ring0 = bwin + kTcWinUnits * kTcUnitBBytes;                    // [decode warp][slot][strip of the pair][tile][8K words]
+  unsigned char* ring0 = bwin + kTcWinBytes;                    // [decode warp][slot][strip of the pair][tile][8K words]
   const uint32_t bwin_addr = smem_u32(bwin);
 
   if (tid == 0) {
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(smem_u32(&s_afull[s]), kTcDecodeWarps / kTcSlots);            // the four quarter warps of one slot
-      mbar_init(smem_u32(&s_freed[s]), 1);                                     // tcgen05.commit
+      mbar_init(smem_u32(&s_freed[s]), kTcLanes / kTcSlots);                   // tcgen05.commit of the slot's two MMA lanes
     }
-    mbar_init(smem_u32(&s_done), 1);
+    for (int g = 0; g < kTcLanes; ++g) mbar_init(smem_u32(&s_done[g]), 1);
     s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (tid < 2 * kTcRows) (&s_amax[0][0])[tid] = 0u;
   if (tid < 2 * kTcRows * 4) (&s_psum[0][0])[tid] = 0;
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(kTcTmemCols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "n"(kTcTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    HTR_TTRACE(tid == 0, 3);
   }
 
   int rb = u_begin / CG, cgi = u_begin - rb * CG;
+  const int unit_b = tc_unit_b_bytes(p.rows), ng_stride = p.rows <= 2 ? 0 : 128, kg_stride = p.rows <= 2 ? 128 : 256;
+  const int win_blocks = kTcWinBytes / unit_b / 2;    // 128-column blocks of activations per window
 
   // ---- packed-word ring of this decode warp: units cs, cs + 2, ... of the CTA's range, R - 1 of them in flight
   const uint32_t ring_addr = smem_u32(ring0) + warp * (R * kSlotBytes);
@@ -236,6 +273,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
   __syncthreads();                                     // barriers, TMEM address, zeroed window statistics
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = s_tmem;
+  HTR_TTRACE(tid == 0, 1);
 
   if (p.prologue == 1) {
     // RMSNorm fused into the activation staging: every CTA finds the row scales itself (the rows are a few KB in L2)
@@ -273,18 +311,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
     // ---- window: units [u, u + seg_units) lie in row block rb and inside kTcBlocks staged 128-column blocks
     const int hb0 = cgi >> 1;
     const int cg_stop = min(CG, cgi + (u_end - u));
-    const int hb1 = min(hb0 + kTcBlocks, (cg_stop + 1) >> 1);
+    const int hb1 = min(hb0 + win_blocks, (cg_stop + 1) >> 1);
     const int seg_cg_end = min(cg_stop, hb1 * 2);
     const int seg_units = seg_cg_end - cgi;
     const int wp = window & 1u;
     const int nblk = hb1 - hb0, items = p.rows * nblk;
 
     // -- stage 1: transform the activations of the window, find the range of every row
-    float xv[kTcRows][4];
-    if (warp < kTcDecodeWarps) {
+    constexpr int kStageRounds = 2;                    // rows x blocks <= 2 x 12 or 4 x 6 = 24 items over 12 warps
+    float xv[kStageRounds][4];
+    {
 #pragma unroll
-      for (int it = 0; it < kTcRows; ++it) {
-        const int item = warp + it * kTcDecodeWarps;   // rows x blocks <= 4 x 6 = 24 items over 8 warps: at most 3 each
+      for (int it = 0; it < kStageRounds; ++it) {
+        const int item = warp + it * kTcWarps;
         xv[it][0] = xv[it][1] = xv[it][2] = xv[it][3] = 0.f;
         if (item < items) {
           const int r = item / nblk, hb = hb0 + item % nblk;
@@ -304,12 +343,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
       }
     }
     __syncthreads();
+    HTR_TTRACE(tid == 0 && window < 4, 4 + 8 * window);
 
     // -- stage 2: four 7-bit planes per activation, splatted over the four bytes of a weight's hash, in the B operand layout
-    if (warp < kTcDecodeWarps) {
+    {
 #pragma unroll
-      for (int it = 0; it < kTcRows; ++it) {
-        const int item = warp + it * kTcDecodeWarps;
+      for (int it = 0; it < kStageRounds; ++it) {
+        const int item = warp + it * kTcWarps;
         if (item < items) {
           const int r = item / nblk, hbi = item % nblk;
           const unsigned mb = s_amax[wp][r];
@@ -329,7 +369,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
           }
           // columns 4 lane .. 4 lane + 3 of block hb: unit 2 hbi + (lane >> 4) of the window, k-group lane & 15, 16 contiguous bytes
           const int ul = 2 * (hb0 + hbi) + (lane >> 4) - 2 * hb0;
-          unsigned char* dst = bwin + ul * kTcUnitBBytes + ((lane & 15) * 2 + (r >> 1)) * 128 + ((r & 1) * 4) * 16;
+          unsigned char* dst = bwin + ul * unit_b + (lane & 15) * kg_stride + (r >> 1) * 128 + ((r & 1) * 4) * 16;
 #pragma unroll
           for (int pl = 0; pl < 4; ++pl)
             *reinterpret_cast<uint4*>(dst + pl * 16) = make_uint4((unsigned)(q[pl][0] & 255) * 0x01010101u, (unsigned)(q[pl][1] & 255) * 0x01010101u,
@@ -344,12 +384,15 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
           }
         }
       }
+      HTR_TTRACE(tid == 0 && window < 4, 8 + 8 * window);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
+      HTR_TTRACE(tid == 0 && window < 4, 9 + 8 * window);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 
+    HTR_TTRACE(tid == 0 && window < 4, 5 + 8 * window);
     // -- main loop of the window
     if (warp < kTcDecodeWarps) {
       const int sp = lane >> 4, r = lane & 15;
@@ -359,41 +402,57 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
         asm volatile("cp.async.wait_group %0;" ::"n"(R - 2) : "memory");   // this unit's words have landed (own copies) ...
         __syncwarp();                                                       // ... and the other lanes'; the previous slot is free
         prefetch(ring_slot == 0 ? R - 1 : ring_slot - 1);
+        HTR_TTRACE(qd == 0 && lane == 0 && i < 16, 36 + 3 * i);
         const int st = i % kTcStages, use = i / kTcStages;
-        if (use > 0 && !__all_sync(kFullWarp, mbar_wait(smem_u32(&s_freed[st]), (uint32_t)(use - 1) & 1u, &s_fail))) { ok = false; break; }
+        // the MMAs that read this stage three units ago must have retired
+        if (use > 0 && !__all_sync(kFullWarp, mbar_wait_hint(smem_u32(&s_freed[st]), (uint32_t)(use - 1) & 1u, &s_fail, 400u))) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        HTR_TTRACE(qd == 0 && lane == 0 && i < 16, 37 + 3 * i);
         const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + ring_slot * kSlotBytes) + sp * (4 * 8 * K);
         const uint32_t taddr = tmem + ((uint32_t)(32 * qd) << 16) + kTcAcol0 + st * kTcStageCols;
 #pragma unroll
         for (int tc = 0; tc < 4; ++tc) {
-          uint32_t V[K + 1], s[32], h[16];
+          uint32_t V[K + 1], st32[32], h[16];
           read_row_words<K>(tiles + tc * (8 * K), r, V);
-          row_states<K>(V, s);
+          row_states<K>(V, st32);
 #pragma unroll
-          for (int c = 0; c < 16; ++c) h[c] = s[c] * kGenMul + kGenAdd;
+          for (int c = 0; c < 16; ++c) h[c] = st32[c] * kGenMul + kGenAdd;
           tmem_store16(taddr + 16 * tc, h);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&s_afull[st]));
+        HTR_TTRACE(qd == 0 && lane == 0 && i < 16, 38 + 3 * i);
         if (++ring_slot == R) ring_slot = 0;
       }
       if (!ok) { s_fail = 1; bad = true; }
     } else if (lane == 0) {
+      // MMA lane ml = 2 g + hf of slot g: the units of the window with the parity of the slot, MMAs 4 hf .. 4 hf + 3 of each,
+      // accumulated in the lane's own 16 TMEM columns.  (A single thread gets an MMA out every 50-150 cycles, whatever its size;
+      // several lanes keep the tensor core fed.)
+      const int ml = warp - kTcDecodeWarps, g = ml >> 1, hf = ml & 1;
+      const uint32_t d_addr = tmem + 16 * ml;
+      const uint32_t desc_hi = (uint32_t)((ng_stride >> 4) & 0x3FFF) | (1u << 14);              // SBO, descriptor version 1
+      const uint32_t desc_lo_const = (uint32_t)((kg_stride >> 4) & 0x3FFF) << 16;              // LBO
+      const uint32_t kk_step = (uint32_t)(2 * kg_stride) >> 4;                                  // one MMA further along k, in 16-byte units
       bool ok = !bad;
-      for (int i = done_i; i < done_i + seg_units && ok; ++i) {
+      uint32_t accumulate = 0u;
+      for (int i = done_i + ((g - done_i) & 1); i < done_i + seg_units && ok; i += kTcSlots) {
         const int st = i % kTcStages, use = i / kTcStages;
-        if (!mbar_wait(smem_u32(&s_afull[st]), (uint32_t)use & 1u, &s_fail)) { ok = false; break; }
+        if (!mbar_wait_hint(smem_u32(&s_afull[st]), (uint32_t)use & 1u, &s_fail, 4000u)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t b_addr = bwin_addr + (uint32_t)(cgi + (i - done_i) - 2 * hb0) * kTcUnitBBytes;
+        HTR_TTRACE(hf == 0 && i < 16, 84 + 2 * i);
+        const uint32_t lo = ((bwin_addr + (uint32_t)(cgi + (i - done_i) - 2 * hb0) * unit_b) >> 4) + desc_lo_const + (uint32_t)(4 * hf) * kk_step;
+        const uint32_t a_addr = tmem + kTcAcol0 + st * kTcStageCols + 32 * hf;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_i8_tmem_a(tmem, tmem + kTcAcol0 + st * kTcStageCols + 8 * kk, umma_desc_kn(b_addr + kk * 512, 256, 128), kIdesc,
-                         (i > done_i || kk) ? 1u : 0u);
+        for (int k4 = 0; k4 < 4; ++k4)
+          umma_i8_tmem_a(d_addr, a_addr + 8 * k4, ((uint64_t)desc_hi << 32) | (lo + (uint32_t)k4 * kk_step), kIdesc, k4 ? 1u : accumulate);
+        accumulate = 1u;
         umma_commit(smem_u32(&s_freed[st]));
+        HTR_TTRACE(hf == 0 && i < 16, 85 + 2 * i);
       }
-      umma_commit(smem_u32(&s_done));                  // covers every MMA issued so far
+      umma_commit(smem_u32(&s_done[ml]));              // covers every MMA this lane has issued so far
       if (!ok) {
         s_fail = 1;
         bad = true;
@@ -401,15 +460,29 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
     }
     __syncwarp();
     // -- drain: the MMAs of the window have retired
-    if (!mbar_wait(smem_u32(&s_done), window & 1u, &s_fail)) {
-      s_fail = 1;
-      mbar_wait_plain(smem_u32(&s_done), window & 1u);                      // let the MMAs in flight retire all the same
-    }
+#pragma unroll
+    for (int g = 0; g < kTcLanes; ++g)
+      if (!mbar_wait(smem_u32(&s_done[g]), window & 1u, &s_fail)) {
+        s_fail = 1;
+        mbar_wait_plain(smem_u32(&s_done[g]), window & 1u);                 // let the MMAs in flight retire all the same
+      }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    done_i += seg_units;
+    HTR_TTRACE(tid == 0 && window < 4, 6 + 8 * window);
     if (warp < kTcDecodeWarps && cs == 0) {
+      // the MMA lanes hold partial sums: add them (the lanes of a slot without a unit in this window hold old values)
       int d[16];
-      tmem_load16_s32(tmem + ((uint32_t)(32 * qd) << 16), d);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) d[j] = 0;
+      const int first_par = done_i & 1;                 // parity of the window's first unit
+#pragma unroll
+      for (int ml = 0; ml < kTcLanes; ++ml) {
+        if (seg_units > 1 || first_par == (ml >> 1)) {  // uniform over the CTA
+          int dl[16];
+          tmem_load16_s32(tmem + ((uint32_t)(32 * qd) << 16) + 16 * ml, dl);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) d[j] += dl[j];
+        }
+      }
 #pragma unroll
       for (int r = 0; r < kTcRows; ++r) {
         if (r < p.rows) {
@@ -425,9 +498,11 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
         }
       }
     }
+    done_i += seg_units;
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();                                   // statistics read, accumulators read: the next window may overwrite both
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    HTR_TTRACE(tid == 0 && window < 4, 7 + 8 * window);
     if (tid < kTcRows) s_amax[wp][tid] = 0u;            // this parity is used again two windows from now
     if (tid < kTcRows * 4) s_psum[wp][tid] = 0;
     ++window;
@@ -521,9 +596,10 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
     if (cgi == CG) { cgi = 0; ++rb; }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
+  HTR_TTRACE(tid == 0, 2);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcTmemCols) : "memory");
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTcTmemCols) : "memory");
   if (tid == 0 && s_fail) atomicAdd(&htr_gemv_tc_failures_dev, 1);
 }
 
