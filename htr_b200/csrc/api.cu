@@ -365,23 +365,38 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   return e ? cuda_fail(e) : HTR_OK;
 }
 
+static int tc_failures(int* count, unsigned* last) {
+  int total = 0, one = 0, e = 0;
+  unsigned where = 0u, w = 0u;
+  if ((e = packed_gemv_tc_failures<2>(&one, &w))) return e;
+  total += one; if (one) where = w;
+  if ((e = packed_gemv_tc_failures<3>(&one, &w))) return e;
+  total += one; if (one) where = w;
+  if ((e = packed_gemv_tc_failures<4>(&one, &w))) return e;
+  total += one; if (one) where = w;
+  if ((e = packed_gemv_tc_failures<5>(&one, &w))) return e;
+  total += one; if (one) where = w;
+  if ((e = packed_gemv_tc_failures<6>(&one, &w))) return e;
+  total += one; if (one) where = w;
+  if ((e = packed_gemv_tc_failures<8>(&one, &w))) return e;
+  total += one; if (one) where = w;
+  *count = total;
+  *last = where;
+  return 0;
+}
+
 int htr_gemv_tc_failures(int* count) {
   if (!count) return HTR_ERR_NULL;
-  int total = 0, one = 0, e = 0;
-  if ((e = packed_gemv_tc_failures<2>(&one))) return cuda_fail(e);
-  total += one;
-  if ((e = packed_gemv_tc_failures<3>(&one))) return cuda_fail(e);
-  total += one;
-  if ((e = packed_gemv_tc_failures<4>(&one))) return cuda_fail(e);
-  total += one;
-  if ((e = packed_gemv_tc_failures<5>(&one))) return cuda_fail(e);
-  total += one;
-  if ((e = packed_gemv_tc_failures<6>(&one))) return cuda_fail(e);
-  total += one;
-  if ((e = packed_gemv_tc_failures<8>(&one))) return cuda_fail(e);
-  total += one;
-  *count = total;
-  return HTR_OK;
+  unsigned where = 0u;
+  const int e = tc_failures(count, &where);
+  return e ? cuda_fail(e) : HTR_OK;
+}
+
+int htr_gemv_tc_last_failure(unsigned* where) {
+  if (!where) return HTR_ERR_NULL;
+  int count = 0;
+  const int e = tc_failures(&count, where);
+  return e ? cuda_fail(e) : HTR_OK;
 }
 
 size_t htr_linear_grouped_workspace_bytes(int count, int m, int n, int K) {

@@ -18,18 +18,27 @@
 // rounding per window.  Results therefore do not depend on the order of anything.
 //
 // Decomposition, split reduction, epilogue, launch overlap: as in packed_gemv.cuh (same GemvParams, same plan, same
-// workspace).  Inside a CTA (288 threads, two CTAs per SM, 256 TMEM columns each):
+// workspace).  Inside a CTA (384 threads at <= 80 registers, two CTAs per SM, 256 TMEM columns each):
 //   * warps 0-7 decode.  Warp = (quarter qd = warp & 3, unit slot cs = warp >> 2); the two slots take alternate units
 //     (unit = 128 rows x 64 columns).  Thread t of quarter qd owns row 32 qd + t of the row block = TMEM lane 32 qd + t,
 //     i.e. one tile row of four consecutive tiles per unit: 64 weights = four tcgen05.st of 16 words.  The packed words travel
 //     global -> shared memory through a per-warp cp.async ring as in the other kernels.
-//   * lane 0 of warp 8 issues the MMAs: per unit 8 instructions of K = 32 bytes (8 columns of A); tcgen05.commit frees the
-//     A stage (three stages of 64 TMEM columns).
-// A window (up to 768 columns) ends with a drain: all MMAs retired, accumulators read out (tcgen05.ld), next window staged.
+//   * lane 0 of warps 8-11 issues the MMAs ("MMA lanes", two per slot): per unit 8 instructions of K = 32 bytes (8 columns
+//     of A), four per lane, into the lane's own 16 accumulator columns; tcgen05.commit frees the A stage (three stages of 64
+//     TMEM columns, used in turn).  One thread gets an MMA of this size out only every 45 cycles at best (measured; ~150 in
+//     this kernel), whatever N up to 64: hence several lanes.
+// A window of activations (1536 columns for one or two rows, 768 for three or four) ends with a drain: all MMAs retired,
+// accumulators read out (tcgen05.ld) and converted, next window staged.
 //
 // Every wait on an mbarrier is bounded; when one expires the CTA stops issuing work, lets copies and MMAs in flight finish
-// (bounded), frees its TMEM columns, counts the failure in a device counter the host can read, and writes NaN results.
+// (bounded), frees its TMEM columns, counts the failure in a device counter the host can read (htr_gemv_tc_failures), and
+// writes NaN results.
+//
+// Status: correct (bit-stable, exact integer accumulation) but slower than the CUDA-core GEMV at every size measured so far;
+// the library therefore uses it only on request (htr_set_gemv_tc / HTR_GEMV_TC=1).
 #pragma once
+#include <cstdio>
+
 #include "packed_gemm_tc.cuh"
 #include "packed_gemv.cuh"
 
@@ -165,6 +174,11 @@ __device__ __forceinline__ void read_row_words(const uint32_t* __restrict__ tile
 
 // failures (expired waits) since the library was loaded, over all launches of this kernel on this device
 static __device__ int htr_gemv_tc_failures_dev = 0;
+// where the last one happened: wait kind (1 freed, 2 operand ready, 3 window done) << 28 | window << 24 | unit of the CTA << 12 | block
+static __device__ unsigned htr_gemv_tc_last_failure_dev = 0u;
+__device__ __forceinline__ void tc_note_failure(unsigned kind, unsigned window, unsigned unit) {
+  htr_gemv_tc_last_failure_dev = (kind << 28) | ((window & 15u) << 24) | ((unit & 4095u) << 12) | (blockIdx.x & 4095u);
+}
 
 #ifdef HTR_GEMV_TC_TRACE
 // timeline probe for experiments: per-CTA %globaltimer stamps, compiled only on request
@@ -177,8 +191,10 @@ __device__ __forceinline__ void tc_stamp(int slot) {
   }
 }
 #define HTR_TTRACE(cond, slot) do { if (cond) tc_stamp(slot); } while (0)
+#define HTR_TFAIL(...) printf(__VA_ARGS__)
 #else
 #define HTR_TTRACE(cond, slot)
+#define HTR_TFAIL(...)
 #endif
 
 template <int K>
@@ -405,7 +421,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
         HTR_TTRACE(qd == 0 && lane == 0 && i < 16, 36 + 3 * i);
         const int st = i % kTcStages, use = i / kTcStages;
         // the MMAs that read this stage three units ago must have retired
-        if (use > 0 && !__all_sync(kFullWarp, mbar_wait_hint(smem_u32(&s_freed[st]), (uint32_t)(use - 1) & 1u, &s_fail, 400u))) { ok = false; break; }
+        if (use > 0 && !__all_sync(kFullWarp, mbar_wait_hint(smem_u32(&s_freed[st]), (uint32_t)(use - 1) & 1u, &s_fail, 400u))) { ok = false; if (lane == 0 && !s_fail) tc_note_failure(1u, window, (unsigned)i); if (lane == 0) HTR_TFAIL("tc fail: freed wait, block %d warp %d unit %d stage %d use %d window %u prior fail %d\n", blockIdx.x, warp, i, st, use, window, s_fail); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         HTR_TTRACE(qd == 0 && lane == 0 && i < 16, 37 + 3 * i);
         const uint32_t* tiles = reinterpret_cast<const uint32_t*>(ring + ring_slot * kSlotBytes) + sp * (4 * 8 * K);
@@ -440,7 +456,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
       uint32_t accumulate = 0u;
       for (int i = done_i + ((g - done_i) & 1); i < done_i + seg_units && ok; i += kTcSlots) {
         const int st = i % kTcStages, use = i / kTcStages;
-        if (!mbar_wait_hint(smem_u32(&s_afull[st]), (uint32_t)use & 1u, &s_fail, 4000u)) { ok = false; break; }
+        if (!mbar_wait_hint(smem_u32(&s_afull[st]), (uint32_t)use & 1u, &s_fail, 400u)) { ok = false; if (!s_fail) tc_note_failure(2u, window, (unsigned)i); HTR_TFAIL("tc fail: a_full wait, block %d lane warp %d unit %d stage %d use %d window %u prior fail %d\n", blockIdx.x, warp, i, st, use, window, s_fail); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         HTR_TTRACE(hf == 0 && i < 16, 84 + 2 * i);
         const uint32_t lo = ((bwin_addr + (uint32_t)(cgi + (i - done_i) - 2 * hb0) * unit_b) >> 4) + desc_lo_const + (uint32_t)(4 * hf) * kk_step;
@@ -463,6 +479,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
 #pragma unroll
     for (int g = 0; g < kTcLanes; ++g)
       if (!mbar_wait(smem_u32(&s_done[g]), window & 1u, &s_fail)) {
+        if (tid == 0 && !s_fail) tc_note_failure(3u, window, (unsigned)g);
+        if (lane == 0) HTR_TFAIL("tc fail: done wait %d, block %d warp %d window %u prior fail %d\n", g, blockIdx.x, warp, window, s_fail);
         s_fail = 1;
         mbar_wait_plain(smem_u32(&s_done[g]), window & 1u);                 // let the MMAs in flight retire all the same
       }
@@ -608,6 +626,6 @@ int launch_packed_gemv_tc(const GemvParams& p, int grid, cudaStream_t stream);
 template <int K>
 int packed_gemv_tc_ctas_per_sm();
 template <int K>
-int packed_gemv_tc_failures(int* count);
+int packed_gemv_tc_failures(int* count, unsigned* last);
 
 }  // namespace htr

@@ -55,8 +55,9 @@ int packed_gemv_tc_ctas_per_sm<HTR_INST_K>() {
 }
 
 template <>
-int packed_gemv_tc_failures<HTR_INST_K>(int* count) {
-  return (int)cudaMemcpyFromSymbol(count, htr_gemv_tc_failures_dev, sizeof(int));
+int packed_gemv_tc_failures<HTR_INST_K>(int* count, unsigned* last) {
+  if (const cudaError_t e = cudaMemcpyFromSymbol(count, htr_gemv_tc_failures_dev, sizeof(int))) return (int)e;
+  return (int)cudaMemcpyFromSymbol(last, htr_gemv_tc_last_failure_dev, sizeof(unsigned));
 }
 
 }  // namespace htr

@@ -217,6 +217,9 @@ int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block)
 /* Number of thread blocks of the tensor-core GEMV (htr_linear with up to four rows) that gave up on a bounded wait since the
  * library was loaded on the current device; such a block writes NaN results.  Zero on a healthy system. */
 int htr_gemv_tc_failures(int* count);
+/* Where the last such block gave up: wait kind (1 = operand stage not released, 2 = operand stage not filled, 3 = window not
+ * finished) << 28 | window of activations << 24 | unit of the block's range << 12 | block index.  0 when there was none. */
+int htr_gemv_tc_last_failure(unsigned* where);
 
 #ifdef __cplusplus
 }
