@@ -331,7 +331,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
     const int seg_cg_end = min(cg_stop, hb1 * 2);
     const int seg_units = seg_cg_end - cgi;
     const int wp = window & 1u;
-    const int nblk = hb1 - hb0, items = p.rows * nblk;
+    // three rows are staged as four (a row of zeros): every B column of the window is then written by this launch
+    const int nblk = hb1 - hb0, items = (p.rows == 3 ? 4 : p.rows) * nblk;
 
     // -- stage 1: transform the activations of the window, find the range of every row
     constexpr int kStageRounds = 2;                    // rows x blocks <= 2 x 12 or 4 x 6 = 24 items over 12 warps
@@ -343,7 +344,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
         xv[it][0] = xv[it][1] = xv[it][2] = xv[it][3] = 0.f;
         if (item < items) {
           const int r = item / nblk, hb = hb0 + item % nblk;
-          const float4 x4 = fused_x(p, p.x, r, hb * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[r] : 1.f);
+          const float4 x4 = r < p.rows ? fused_x(p, p.x, r, hb * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[r] : 1.f) : make_float4(0.f, 0.f, 0.f, 0.f);
           const unsigned sg = sign_nibble(p.su, hb * 32 + lane);
           float v[4] = {flip(x4.x, sg & 1u), flip(x4.y, (sg >> 1) & 1u), flip(x4.z, (sg >> 2) & 1u), flip(x4.w, sg >> 3)};
           wht128(v, lane);
