@@ -66,11 +66,6 @@ __host__ __device__ constexpr int gemv_tc_smem_bytes(int K) {
   return kTcWinBytes + kTcDecodeWarps * tc_ring_slots(K) * tc_slot_bytes(K) + 128 + 64;
 }
 
-__device__ __forceinline__ uint64_t umma_desc_kn(uint32_t smem_addr, int lbo_bytes, int sbo_bytes) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) | ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) |
-         (1ull << 46);
-}
-
 // D[128 x 16] (+)= A[128 x 32 u8, TMEM] * B[32 x 16 s8, shared memory]
 __device__ __forceinline__ void umma_i8_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
