@@ -3,6 +3,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "packed_gemv_mma.cuh"
 #include "packed_gemv_tc.cuh"
 
 namespace htr {
@@ -65,13 +66,27 @@ static int gemv_tc_ctas_per_sm(int K) {
   return -1;
 }
 
-// HTR_GEMV_TC=0 in the environment keeps every batch size on the CUDA-core GEMV (for A/B timing and as a fallback switch)
-static bool gemv_tc_enabled() {
-  static const bool on = [] {
+static int gemv_mma_ctas_per_sm(int K, int rows) {
+  switch (K) {
+    case 2: return packed_gemv_mma_ctas_per_sm<2>(rows);
+    case 3: return packed_gemv_mma_ctas_per_sm<3>(rows);
+    case 4: return packed_gemv_mma_ctas_per_sm<4>(rows);
+    case 5: return packed_gemv_mma_ctas_per_sm<5>(rows);
+    case 6: return packed_gemv_mma_ctas_per_sm<6>(rows);
+    case 8: return packed_gemv_mma_ctas_per_sm<8>(rows);
+  }
+  return -1;
+}
+
+// Which kernel serves single problems of up to four activation rows: 0 = CUDA-core GEMV, 1 = tcgen05 GEMV (A operand in tensor
+// memory), 2 = warp-MMA GEMV.  HTR_GEMV_TC in the environment overrides the build default.
+static int gemv_kind_default() {
+  static const int kind = [] {
     const char* v = std::getenv("HTR_GEMV_TC");
-    return v ? v[0] != '0' : HTR_GEMV_TC_DEFAULT != 0;
+    const int k = v ? std::atoi(v) : HTR_GEMV_TC_DEFAULT;
+    return k < 0 || k > 2 ? 0 : k;
   }();
-  return on;
+  return kind;
 }
 
 bool gemv_overlap_enabled() {
@@ -119,10 +134,20 @@ static int cached_tc_occupancy(int dev, int K) {
 }
 
 // the tensor-core GEMV serves single problems of up to four activation rows
-static int g_tc_override = -1;                         // -1: environment / build default, 0: off, 1: on
-static bool use_tc(int M) { return (g_tc_override >= 0 ? g_tc_override != 0 : gemv_tc_enabled()) && M <= kTcRows; }
+static int cached_mma_occupancy(int dev, int K, int rows) {
+  static int cache[64][9][2] = {{{0}}};
+  static std::mutex mu;
+  if (dev < 0 || dev >= 64) return gemv_mma_ctas_per_sm(K, rows);
+  std::lock_guard<std::mutex> lock(mu);
+  int& slot = cache[dev][K][rows <= 2 ? 0 : 1];
+  if (slot == 0) slot = gemv_mma_ctas_per_sm(K, rows);
+  return slot;
+}
 
-static int make_plan(int M, int m, int n, int K, Plan* out, bool tc = false) {
+static int g_tc_override = -1;                         // -1: environment / build default, else the kind
+static int gemv_kind(int M) { return M <= kTcRows ? (g_tc_override >= 0 ? g_tc_override : gemv_kind_default()) : 0; }
+
+static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail((int)e);
@@ -130,7 +155,8 @@ static int make_plan(int M, int m, int n, int K, Plan* out, bool tc = false) {
   if (sms <= 0) return cuda_fail((int)cudaErrorInvalidDevice);
   Plan pl;
   pl.rows_t = template_rows(M);
-  int per_sm = tc ? cached_tc_occupancy(dev, K) : g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
+  int per_sm = kind == 1 ? cached_tc_occupancy(dev, K) : kind == 2 ? cached_mma_occupancy(dev, K, M)
+               : g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
   if (per_sm <= 0) return cuda_fail((int)cudaErrorLaunchOutOfResources);
   pl.rbs = m / 128;
   pl.cg = n / 64;
@@ -194,7 +220,7 @@ int htr_last_cuda_error(void) { return t_last_cuda; }
 int htr_version(void) { return 100; }
 
 void htr_set_gemv_ctas_per_sm(int ctas) { g_ctas_override = ctas > 0 ? ctas : 0; }
-void htr_set_gemv_tc(int mode) { g_tc_override = mode < 0 ? -1 : mode != 0; }
+void htr_set_gemv_tc(int mode) { g_tc_override = mode < 0 || mode > 2 ? -1 : mode; }
 
 int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
@@ -223,9 +249,9 @@ size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
   Plan pl;
   if (make_plan(M, m, n, K, &pl) != HTR_OK) return 0;
   size_t slots = (size_t)pl.slots;
-  if (use_tc(M)) {                                     // either kernel may serve the call: size for both
+  if (gemv_kind(M)) {                                  // either kernel may serve the call: size for both
     Plan tc;
-    if (make_plan(M, m, n, K, &tc, true) != HTR_OK) return 0;
+    if (make_plan(M, m, n, K, &tc, gemv_kind(M)) != HTR_OK) return 0;
     if ((size_t)tc.slots > slots) slots = (size_t)tc.slots;
   }
   return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * sizeof(float);
@@ -235,7 +261,7 @@ int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block)
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return HTR_ERR_BAD_SHAPE;
   Plan pl;
-  const int rc = make_plan(M, m, n, K, &pl, use_tc(M));
+  const int rc = make_plan(M, m, n, K, &pl, gemv_kind(M));
   if (rc != HTR_OK) return rc;
   if (grid) *grid = pl.grid;
   if (slots_per_block) *slots_per_block = pl.slots;
@@ -298,8 +324,8 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
     return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
   Plan pl;
-  const bool tc = use_tc(M);
-  const int rc = make_plan(M, m, n, K, &pl, tc);
+  const int kind = gemv_kind(M);
+  const int rc = make_plan(M, m, n, K, &pl, kind);
   if (rc != HTR_OK) return rc;
   const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
@@ -343,7 +369,18 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int e = 0;
-  if (tc) {
+  if (kind == 2) {
+    switch (K) {
+      case 2: e = launch_packed_gemv_mma<2>(p, pl.grid, st); break;
+      case 3: e = launch_packed_gemv_mma<3>(p, pl.grid, st); break;
+      case 4: e = launch_packed_gemv_mma<4>(p, pl.grid, st); break;
+      case 5: e = launch_packed_gemv_mma<5>(p, pl.grid, st); break;
+      case 6: e = launch_packed_gemv_mma<6>(p, pl.grid, st); break;
+      case 8: e = launch_packed_gemv_mma<8>(p, pl.grid, st); break;
+    }
+    return e ? cuda_fail(e) : HTR_OK;
+  }
+  if (kind == 1) {
     switch (K) {
       case 2: e = launch_packed_gemv_tc<2>(p, pl.grid, st); break;
       case 3: e = launch_packed_gemv_tc<3>(p, pl.grid, st); break;

@@ -1,7 +1,8 @@
-"""The tensor-core GEMV (htr_linear with up to four activation rows behind htr_set_gemv_tc(1)): parity with the CPU oracle
-and with the CUDA-core GEMV, through the same entry points.
+"""The two tensor-core GEMVs (htr_linear with up to four activation rows behind htr_set_gemv_tc: 1 = tcgen05 with the hash
+words in tensor memory, 2 = warp-level mma.sync straight from the hash registers): parity with the CPU oracle and with the
+CUDA-core GEMV, through the same entry points.
 
-The kernel works in exact integers (hash bytes x 7-bit activation planes, s32 accumulators), so beyond the tolerances of
+Both kernels work in exact integers (hash bytes x 7-bit activation planes, s32 accumulators), so beyond the tolerances of
 tests/test_gpu_parity.py it must be bit-stable from run to run and must agree with the CUDA-core GEMV to float32 rounding.
   float32 activations/outputs: norm-relative error <= 1e-5 against the oracle, <= 2e-6 against the CUDA-core GEMV
   bf16 outputs:                the tolerances of tests/test_gpu_parity.py
@@ -23,11 +24,15 @@ def dev():
     return torch.device("cuda:0")
 
 
-@pytest.fixture(autouse=True)
-def tensor_core_gemv():
+KIND = [1]
+
+
+@pytest.fixture(autouse=True, params=(1, 2), ids=("tcgen05", "mma_sync"))
+def tensor_core_gemv(request):
     from htr_b200 import _lib
 
-    _lib.lib.htr_set_gemv_tc(1)
+    KIND[0] = request.param
+    _lib.lib.htr_set_gemv_tc(request.param)
     yield
     _lib.lib.htr_set_gemv_tc(-1)
 
@@ -59,7 +64,7 @@ def cuda_core(fn):
     try:
         return fn()
     finally:
-        _lib.lib.htr_set_gemv_tc(1)
+        _lib.lib.htr_set_gemv_tc(KIND[0])
 
 
 @pytest.mark.parametrize("K", (2, 3, 4, 5))
@@ -192,4 +197,4 @@ def test_plan_and_workspace_cover_both_kernels(dev):
         need = _lib.lib.htr_linear_workspace_bytes(M, m, n, K)
         rows_t = 1 if M <= 1 else 2 if M <= 2 else 4
         assert need >= _lib.lib.htr_linear_counter_bytes(m) + (m // 128) * slots.value * rows_t * 128 * 4
-        assert 1 <= grid.value <= 2 * torch.cuda.get_device_properties(dev).multi_processor_count
+        assert 1 <= grid.value <= 3 * torch.cuda.get_device_properties(dev).multi_processor_count
