@@ -37,8 +37,15 @@ template <int NS>
 struct MmaWinUnits {
   static constexpr int value = NS == 1 ? 16 : 8;
 };
+// Words between the tiles of a warp's ring slot.  The four lanes of a quad read the same row pair of four different tiles, so
+// with the tiles back to back (8K words) their loads would hit the same banks; a few words of padding spread them out
+// (wavefronts per lane unit: K2 6 -> 4, K4 20 -> 8, K6 14 -> 8, K8 40 -> 20; K3 and K5 are conflict-free as they are).
+template <int K>
+struct MmaTileStride {
+  static constexpr int value = 8 * K + (K == 8 ? 4 : K % 2 == 0 ? 8 : 0);
+};
 template <int K, int NS>
-constexpr int gemv_mma_smem_bytes() { return MmaWinUnits<NS>::value * NS * 2048 + kRing * kGemvWarps * 4 * (32 * K); }
+constexpr int gemv_mma_smem_bytes() { return MmaWinUnits<NS>::value * NS * 2048 + kRing * kGemvWarps * 4 * (4 * MmaTileStride<K>::value); }
 
 __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -51,7 +58,7 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? 3 : 2)) packed_gemv_m
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   constexpr int kWinUnits = MmaWinUnits<NS>::value, kWinBlocks = kWinUnits / 2;
   unsigned char* bwin = dyn_smem;                                                   // [unit][set][4 word groups][32 reader lanes][16 B]
-  uint32_t* ring = reinterpret_cast<uint32_t*>(dyn_smem + kWinUnits * NS * 2048);  // [kRing][warps][4 tiles][8K]
+  uint32_t* ring = reinterpret_cast<uint32_t*>(dyn_smem + kWinUnits * NS * 2048);  // [kRing][warps][4 tiles][tile stride]
   __shared__ int s_arrival;
   __shared__ unsigned s_amax[kMmaRows];
   __shared__ int s_psum[kMmaRows * 4];
@@ -71,12 +78,12 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? 3 : 2)) packed_gemv_m
     u_begin = (int)((long long)blockIdx.x * U / G);
     u_end = (int)(((long long)blockIdx.x + 1) * U / G);
   }
-  constexpr int kTileWords = 8 * K, kTileBytes = 32 * K, kTileChunks = 2 * K;
-  constexpr int kStageBytes = kGemvWarps * 4 * kTileBytes;
+  constexpr int kTileStride = MmaTileStride<K>::value, kTileBytes = 32 * K, kTileChunks = 2 * K;
+  constexpr int kStageBytes = kGemvWarps * 4 * kTileStride * 4;
 
   // ring slot of this warp: the four tiles of its strip; copy roles: tile lane >> 3, 16-byte chunk lane & 7
-  const uint32_t* my_ring = ring + (warp * 4) * kTileWords;
-  const uint32_t ring_dst = (uint32_t)__cvta_generic_to_shared(my_ring + (lane >> 3) * kTileWords) + (lane & 7) * 16;
+  const uint32_t* my_ring = ring + (warp * 4) * kTileStride;
+  const uint32_t ring_dst = (uint32_t)__cvta_generic_to_shared(my_ring + (lane >> 3) * kTileStride) + (lane & 7) * 16;
 
   int rb = u_begin / CG, cgi = u_begin - rb * CG;
   const char* lane_base = reinterpret_cast<const char*>(p.qw) + ((size_t)(rb * 8 + warp) * nt + (size_t)(4 * cgi + (lane >> 3))) * kTileBytes + (lane & 7) * 16;
@@ -220,7 +227,7 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? 3 : 2)) packed_gemv_m
       uint32_t V[K + 1];
       async_wait<kDepth - 1>();
       __syncwarp();
-      read_unit_words<K>(reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_ring) + stage_bytes) + c * kTileWords, g, V);
+      read_unit_words<K>(reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_ring) + stage_bytes) + c * kTileStride, g, V);
       issue(refill_bytes);
       refill_bytes = stage_bytes;
       stage_bytes = (stage_bytes + kStageBytes == kRing * kStageBytes) ? 0 : stage_bytes + kStageBytes;
