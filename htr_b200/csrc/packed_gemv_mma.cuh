@@ -28,6 +28,10 @@
 #pragma once
 #include "packed_gemv.cuh"
 
+#ifndef HTR_MMA_CTAS
+#define HTR_MMA_CTAS 3
+#endif
+
 namespace htr {
 
 constexpr int kMmaRows = 4;                              // activation rows per launch (two per MMA set)
@@ -54,7 +58,7 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
 }
 
 template <int K, int NS>
-__global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? 3 : 2)) packed_gemv_mma_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) packed_gemv_mma_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   constexpr int kWinUnits = MmaWinUnits<NS>::value, kWinBlocks = kWinUnits / 2;
   unsigned char* bwin = dyn_smem;                                                   // [unit][set][4 word groups][32 reader lanes][16 B]
