@@ -145,13 +145,7 @@ static int cached_mma_occupancy(int dev, int K, int rows) {
 }
 
 static int g_tc_override = -1;                         // -1: environment / build default, else the kind
-// The tcgen05 kernel is used for one or two rows only: its three- and four-row form (both n-groups of the B operand stored) ran
-// into expired waits once in about a thousand overlapped launches, cause unknown; those row counts stay on the CUDA-core kernel.
-static int gemv_kind(int M) {
-  if (M > kTcRows) return 0;
-  const int kind = g_tc_override >= 0 ? g_tc_override : gemv_kind_default();
-  return kind == 1 && M > 2 ? 0 : kind;
-}
+static int gemv_kind(int M) { return M <= kTcRows ? (g_tc_override >= 0 ? g_tc_override : gemv_kind_default()) : 0; }
 
 static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
   int dev = 0;

@@ -24,8 +24,8 @@
 //     i.e. one tile row of four consecutive tiles per unit: 64 weights = four tcgen05.st of 16 words.  The packed words travel
 //     global -> shared memory through a per-warp cp.async ring as in the other kernels.
 //   * lane 0 of warps 8-11 issues the MMAs ("MMA lanes", two per slot): per unit 8 instructions of K = 32 bytes (8 columns
-//     of A), four per lane, into the lane's own 16 accumulator columns; tcgen05.commit frees the A stage (three stages of 64
-//     TMEM columns, used in turn).  One thread gets an MMA of this size out only every 45 cycles at best (measured; ~150 in
+//     of A), four per lane, into the lane's own 16 accumulator columns (32 columns apart); tcgen05.commit frees the A stage
+//     (two stages of 64 TMEM columns, used in turn).  One thread gets an MMA of this size out only every 45 cycles at best (measured; ~150 in
 //     this kernel), whatever N up to 64: hence several lanes.
 // A window of activations (1536 columns for one or two rows, 768 for three or four) ends with a drain: all MMAs retired,
 // accumulators read out (tcgen05.ld) and converted, next window staged.
@@ -49,9 +49,13 @@ constexpr int kTcSlots = 2;                                // decode warp groups
 constexpr int kTcLanes = 2 * kTcSlots;                     // MMA lanes: two per slot, each issues half of a unit's MMAs
 constexpr int kTcWarps = kTcDecodeWarps + kTcLanes;
 constexpr int kTcThreads = kTcWarps * 32;                 // 384: 3 warps per scheduler, two CTAs per SM at <= 80 registers
-constexpr int kTcStages = 3;                               // A stages in TMEM, used in turn by the units of a CTA
+// TMEM columns between the accumulators of two MMA lanes.  Each accumulator is 16 columns wide, but they must not share a
+// 32-column granule: with a spacing of 16, MMAs issued concurrently by two threads into neighbouring accumulators gave a wrong
+// sum about once in 5000 launches and, rarely, an MMA that never completed (24000 launches each way: 5 + 1 against 0 + 0).
+constexpr int kTcDStride = 32;
+constexpr int kTcStages = 2;                               // A stages in TMEM, used in turn by the units of a CTA
 constexpr int kTcStageCols = 64;                           // one unit: 64 weights per row
-constexpr int kTcAcol0 = 64;                               // first A column (accumulators: 16 columns per MMA lane in columns 0..63)
+constexpr int kTcAcol0 = 4 * kTcDStride;                   // first A column (the accumulators of the four MMA lanes come first)
 constexpr int kTcTmemCols = 256;
 constexpr int kTcWinBytes = 48 * 1024;                     // B operand of one window of activations
 constexpr int kTcRows = 4;                                 // activation rows per launch (x 4 planes = 16 accumulator columns)
@@ -444,7 +448,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
       // accumulated in the lane's own 16 TMEM columns.  (A single thread gets an MMA out every 50-150 cycles, whatever its size;
       // several lanes keep the tensor core fed.)
       const int ml = warp - kTcDecodeWarps, g = ml >> 1, hf = ml & 1;
-      const uint32_t d_addr = tmem + 16 * ml;
+      const uint32_t d_addr = tmem + kTcDStride * ml;
       const uint32_t desc_hi = (uint32_t)((ng_stride >> 4) & 0x3FFF) | (1u << 14);              // SBO, descriptor version 1
       const uint32_t desc_lo_const = (uint32_t)((kg_stride >> 4) & 0x3FFF) << 16;              // LBO
       const uint32_t kk_step = (uint32_t)(2 * kg_stride) >> 4;                                  // one MMA further along k, in 16-byte units
@@ -492,7 +496,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) packed_gemv_tc_kernel(const Gem
       for (int ml = 0; ml < kTcLanes; ++ml) {
         if (seg_units > 1 || first_par == (ml >> 1)) {  // uniform over the CTA
           int dl[16];
-          tmem_load16_s32(tmem + ((uint32_t)(32 * qd) << 16) + 16 * ml, dl);
+          tmem_load16_s32(tmem + ((uint32_t)(32 * qd) << 16) + kTcDStride * ml, dl);
 #pragma unroll
           for (int j = 0; j < 16; ++j) d[j] += dl[j];
         }

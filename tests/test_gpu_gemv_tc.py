@@ -1,7 +1,6 @@
 """The two tensor-core GEMVs (htr_linear with up to four activation rows behind htr_set_gemv_tc: 1 = tcgen05 with the hash
 words in tensor memory, 2 = warp-level mma.sync straight from the hash registers): parity with the CPU oracle and with the
-CUDA-core GEMV, through the same entry points.  (Kind 1 serves one or two rows; with three or four the library keeps the
-CUDA-core kernel, so those cases of the tcgen05 parameter check just that.)
+CUDA-core GEMV, through the same entry points.
 
 Both kernels work in exact integers (hash bytes x 7-bit activation planes, s32 accumulators), so beyond the tolerances of
 tests/test_gpu_parity.py it must be bit-stable from run to run and must agree with the CUDA-core GEMV to float32 rounding.
