@@ -13,7 +13,7 @@ int run_dequant_w(int K, const uint32_t* qw, const __half* scales, const uint8_t
                   int out_dtype, int mt, int nt, cudaStream_t st);
 
 #ifndef HTR_GEMV_TC_DEFAULT
-#define HTR_GEMV_TC_DEFAULT 0
+#define HTR_GEMV_TC_DEFAULT -1
 #endif
 
 static thread_local int t_last_cuda = 0;
@@ -66,25 +66,25 @@ static int gemv_tc_ctas_per_sm(int K) {
   return -1;
 }
 
-static int gemv_mma_ctas_per_sm(int K, int rows) {
+static int gemv_mma_ctas_per_sm(int K, int rows, int dtype) {
   switch (K) {
-    case 2: return packed_gemv_mma_ctas_per_sm<2>(rows);
-    case 3: return packed_gemv_mma_ctas_per_sm<3>(rows);
-    case 4: return packed_gemv_mma_ctas_per_sm<4>(rows);
-    case 5: return packed_gemv_mma_ctas_per_sm<5>(rows);
-    case 6: return packed_gemv_mma_ctas_per_sm<6>(rows);
-    case 8: return packed_gemv_mma_ctas_per_sm<8>(rows);
+    case 2: return packed_gemv_mma_ctas_per_sm<2>(rows, dtype);
+    case 3: return packed_gemv_mma_ctas_per_sm<3>(rows, dtype);
+    case 4: return packed_gemv_mma_ctas_per_sm<4>(rows, dtype);
+    case 5: return packed_gemv_mma_ctas_per_sm<5>(rows, dtype);
+    case 6: return packed_gemv_mma_ctas_per_sm<6>(rows, dtype);
+    case 8: return packed_gemv_mma_ctas_per_sm<8>(rows, dtype);
   }
   return -1;
 }
 
 // Which kernel serves single problems of up to four activation rows: 0 = CUDA-core GEMV, 1 = tcgen05 GEMV (A operand in tensor
-// memory), 2 = warp-MMA GEMV.  HTR_GEMV_TC in the environment overrides the build default.
+// memory), 2 = warp-MMA GEMV, -1 = by measurement (below).  HTR_GEMV_TC in the environment overrides the build default.
 static int gemv_kind_default() {
   static const int kind = [] {
     const char* v = std::getenv("HTR_GEMV_TC");
     const int k = v ? std::atoi(v) : HTR_GEMV_TC_DEFAULT;
-    return k < 0 || k > 2 ? 0 : k;
+    return k < -1 || k > 2 ? -1 : k;
   }();
   return kind;
 }
@@ -134,20 +134,29 @@ static int cached_tc_occupancy(int dev, int K) {
 }
 
 // the tensor-core GEMV serves single problems of up to four activation rows
-static int cached_mma_occupancy(int dev, int K, int rows) {
+static int cached_mma_occupancy(int dev, int K, int rows, int dtype) {
   static int cache[64][9][2] = {{{0}}};
   static std::mutex mu;
-  if (dev < 0 || dev >= 64) return gemv_mma_ctas_per_sm(K, rows);
+  if (dev < 0 || dev >= 64) return gemv_mma_ctas_per_sm(K, rows, dtype);
   std::lock_guard<std::mutex> lock(mu);
-  int& slot = cache[dev][K][rows <= 2 ? 0 : 1];
-  if (slot == 0) slot = gemv_mma_ctas_per_sm(K, rows);
+  int& slot = cache[dev][K][mma_one_set(rows, dtype) ? 0 : 1];
+  if (slot == 0) slot = gemv_mma_ctas_per_sm(K, rows, dtype);
   return slot;
 }
 
 static int g_tc_override = -1;                         // -1: environment / build default, else the kind
-static int gemv_kind(int M) { return M <= kTcRows ? (g_tc_override >= 0 ? g_tc_override : gemv_kind_default()) : 0; }
+// Measured policy (4096x12288 K4, bf16): one row 12.2 us on the CUDA-core kernel against 12.5 on the warp-MMA kernel; two rows 15.8
+// against 14.3 (one MMA set serves both); three and four rows of 16-bit activations 21.4 / 22.0 against 16.2 / 17.9 (two planes per
+// activation, one set); three and four float32 or fp16 rows need two sets of four planes and lose (22.1 against 25.6).
+static int gemv_kind(int M, int dtype = HTR_DTYPE_BF16) {
+  if (M > kTcRows) return 0;
+  const int kind = g_tc_override >= 0 ? g_tc_override : gemv_kind_default();
+  if (kind >= 0) return kind;
+  // (fp16 results carry 11 bits: there the two-plane form would double the error of the output rounding, so fp16 keeps four planes)
+  return M == 2 || (M > 2 && dtype == HTR_DTYPE_BF16) ? 2 : 0;
+}
 
-static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
+static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0, int dtype = HTR_DTYPE_BF16) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail((int)e);
@@ -155,7 +164,7 @@ static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
   if (sms <= 0) return cuda_fail((int)cudaErrorInvalidDevice);
   Plan pl;
   pl.rows_t = template_rows(M);
-  int per_sm = kind == 1 ? cached_tc_occupancy(dev, K) : kind == 2 ? cached_mma_occupancy(dev, K, M)
+  int per_sm = kind == 1 ? cached_tc_occupancy(dev, K) : kind == 2 ? cached_mma_occupancy(dev, K, M, dtype)
                : g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
   if (per_sm <= 0) return cuda_fail((int)cudaErrorLaunchOutOfResources);
   pl.rbs = m / 128;
@@ -220,7 +229,7 @@ int htr_last_cuda_error(void) { return t_last_cuda; }
 int htr_version(void) { return 100; }
 
 void htr_set_gemv_ctas_per_sm(int ctas) { g_ctas_override = ctas > 0 ? ctas : 0; }
-void htr_set_gemv_tc(int mode) { g_tc_override = mode < 0 || mode > 2 ? -1 : mode; }
+void htr_set_gemv_tc(int mode) { g_tc_override = mode < 0 || mode > 2 ? -1 : mode; }   // -1: back to the default
 
 int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
@@ -249,9 +258,11 @@ size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
   Plan pl;
   if (make_plan(M, m, n, K, &pl) != HTR_OK) return 0;
   size_t slots = (size_t)pl.slots;
-  if (gemv_kind(M)) {                                  // either kernel may serve the call: size for both
+  for (int dtype = HTR_DTYPE_BF16; dtype <= HTR_DTYPE_F32; ++dtype) {   // any of the kernels may serve the call: size for all
+    const int kind = gemv_kind(M, dtype);
+    if (kind == 0) continue;
     Plan tc;
-    if (make_plan(M, m, n, K, &tc, gemv_kind(M)) != HTR_OK) return 0;
+    if (make_plan(M, m, n, K, &tc, kind, dtype) != HTR_OK) return 0;
     if ((size_t)tc.slots > slots) slots = (size_t)tc.slots;
   }
   return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * sizeof(float);
@@ -324,8 +335,8 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
     return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
   Plan pl;
-  const int kind = gemv_kind(M);
-  const int rc = make_plan(M, m, n, K, &pl, kind);
+  const int kind = gemv_kind(M, dtype);
+  const int rc = make_plan(M, m, n, K, &pl, kind, dtype);
   if (rc != HTR_OK) return rc;
   const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;

@@ -72,6 +72,9 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;               // consumer roles: row pair of the strip, tile column of the unit
+  // planes per activation: four (27 bits), or two (13 bits below the largest value of the window: enough for bf16, whose
+  // results are rounded to 8 bits) when an MMA set has to serve four rows instead of two
+  const int P = p.rows > 2 * NS ? 2 : 4, RPS = 8 / P;
   const int U = p.units, G = gridDim.x, CG = p.cg, nt = p.nt, n = nt * 16, m = p.mt * 16;
   int u_begin, u_end;
   if (p.split > 0) {
@@ -155,12 +158,13 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
     const int hb1 = min(hb0 + kWinBlocks, (cg_stop + 1) >> 1);
     const int seg_cg_end = min(cg_stop, hb1 * 2);
     const int seg_units = seg_cg_end - cgi;
-    const int nblk = hb1 - hb0, items = p.rows * nblk;  // <= 2 x 8 or 4 x 4 = 16 items over 8 warps
+    const int nblk = hb1 - hb0, items = p.rows * nblk;  // <= 4 x 8 = 32 items over 8 warps (two planes), else <= 16
+    constexpr int kRounds = NS == 1 ? 4 : 2;
 
     // -- stage 1: transform the activations of the window, find the range of every row
-    float xv[2][4];
+    float xv[kRounds][4];
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
+    for (int it = 0; it < kRounds; ++it) {
       const int item = warp + it * kGemvWarps;
       xv[it][0] = xv[it][1] = xv[it][2] = xv[it][3] = 0.f;
       if (item < items) {
@@ -180,9 +184,9 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
     }
     __syncthreads();
 
-    // -- stage 2: four 7-bit planes per activation, splatted over a word, laid out per reader lane
+    // -- stage 2: 7-bit planes of every activation, splatted over a word, laid out per reader lane
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
+    for (int it = 0; it < kRounds; ++it) {
       const int item = warp + it * kGemvWarps;
       if (item < items) {
         const int r = item / nblk, hbi = item % nblk;
@@ -202,14 +206,15 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
           }
         }
         // this lane holds columns 4 lane .. 4 lane + 3 of the block: unit lane >> 4, tile (lane >> 2) & 3, word group lane & 3;
-        // reader lane (B column n, tile) = 4 n + tile, with n = 4 (r & 1) + plane, in MMA set r >> 1
+        // reader lane (B column n, tile) = 4 n + tile, with n = P (r % RPS) + plane, in MMA set r / RPS
         const int ul = 2 * hbi + (lane >> 4);
-        unsigned char* dst = bwin + ((((ul * NS + (r >> 1)) * 4 + (lane & 3)) * 32 + ((lane >> 2) & 3)) * 16);
+        unsigned char* dst = bwin + ((((ul * NS + r / RPS) * 4 + (lane & 3)) * 32 + ((lane >> 2) & 3)) * 16);
 #pragma unroll
         for (int pl = 0; pl < 4; ++pl)
-          *reinterpret_cast<uint4*>(dst + (4 * (4 * (r & 1) + pl)) * 16) =
-              make_uint4((unsigned)(q[pl][0] & 255) * 0x01010101u, (unsigned)(q[pl][1] & 255) * 0x01010101u,
-                         (unsigned)(q[pl][2] & 255) * 0x01010101u, (unsigned)(q[pl][3] & 255) * 0x01010101u);
+          if (pl < P)
+            *reinterpret_cast<uint4*>(dst + (4 * (P * (r % RPS) + pl)) * 16) =
+                make_uint4((unsigned)(q[pl][0] & 255) * 0x01010101u, (unsigned)(q[pl][1] & 255) * 0x01010101u,
+                           (unsigned)(q[pl][2] & 255) * 0x01010101u, (unsigned)(q[pl][3] & 255) * 0x01010101u);
         const int cgu = 2 * (hb0 + hbi) + (lane >> 4);
         const bool mine = cgu >= cgi && cgu < seg_cg_end;
 #pragma unroll
@@ -254,21 +259,25 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
       bunit += NS * 2048;
     }
 
-    // -- the window's integers leave for float: lane (g, c) holds planes 2 (c & 1), 2 (c & 1) + 1 of activation row 2t + (c >> 1)
+    // -- the window's integers leave for float.  Four planes: lane (g, c) holds planes 2 (c & 1), 2 (c & 1) + 1 of activation row
+    // 2t + (c >> 1), the other two sit in the neighbouring lane.  Two planes: both planes of activation row 4t + c.
 #pragma unroll
     for (int t = 0; t < NS; ++t) {
-      const int r = 2 * t + (c >> 1), p0 = 2 * (c & 1);
+      const int r = P == 4 ? 2 * t + (c >> 1) : 4 * t + c, p0 = P == 4 ? 2 * (c & 1) : 0;
       const int rr_ok = r < p.rows;
       const int ra = rr_ok ? r : 0;
-      const long long hi = (c & 1) ? 1ll : 16384ll;    // 128^2 for planes 0, 1
+      const long long hi = (P == 4 && (c & 1) == 0) ? 16384ll : 1ll;    // 128^2 for planes 0, 1 of four
       long long v0 = ((long long)(d[t][0] - 510 * s_psum[ra * 4 + p0]) * 128 + (long long)(d[t][1] - 510 * s_psum[ra * 4 + p0 + 1])) * hi;
       long long v1 = ((long long)(d[t][2] - 510 * s_psum[ra * 4 + p0]) * 128 + (long long)(d[t][3] - 510 * s_psum[ra * 4 + p0 + 1])) * hi;
-      v0 += __shfl_xor_sync(kFullWarp, v0, 1);
-      v1 += __shfl_xor_sync(kFullWarp, v1, 1);
+      if (P == 4) {
+        v0 += __shfl_xor_sync(kFullWarp, v0, 1);
+        v1 += __shfl_xor_sync(kFullWarp, v1, 1);
+      }
       const unsigned mb = s_amax[ra];
       int ex = (int)(mb >> 23) - 127;
       ex = ex < -100 ? -100 : ex;
-      const double w = __longlong_as_double((long long)(1023 - 21 - 5 + ex) << 52);   // 2^-21 / sc
+      // 1 / (sc * 128^(P-1)), sc = 2^(5 - ex)
+      const double w = __longlong_as_double((long long)(1023 - 7 * (P - 1) - 5 + ex) << 52);
       if (rr_ok) {
         accf[t][0] += mb < 0x7F800000u ? (float)((double)v0 * w) : __uint_as_float(0x7FC00000u);
         accf[t][1] += mb < 0x7F800000u ? (float)((double)v1 * w) : __uint_as_float(0x7FC00000u);
@@ -283,12 +292,14 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
     if (cgi < CG && u < u_end) { __syncthreads(); continue; }   // same row block, next window (zeroed statistics visible)
 
     // ---- this CTA's contribution to row block rb is complete
-    if ((c & 1) == 0) {
+    if (P == 2 || (c & 1) == 0) {
 #pragma unroll
       for (int t = 0; t < NS; ++t) {
-        const int r = 2 * t + (c >> 1);
-        ytil[r * 128 + warp * 16 + 2 * g] = accf[t][0] * kInvSqrt128;
-        ytil[r * 128 + warp * 16 + 2 * g + 1] = accf[t][1] * kInvSqrt128;
+        const int r = P == 4 ? 2 * t + (c >> 1) : 4 * t + c;
+        if (r < kMmaRows) {
+          ytil[r * 128 + warp * 16 + 2 * g] = accf[t][0] * kInvSqrt128;
+          ytil[r * 128 + warp * 16 + 2 * g + 1] = accf[t][1] * kInvSqrt128;
+        }
       }
     }
 #pragma unroll
@@ -374,6 +385,8 @@ __global__ void __launch_bounds__(kGemvThreads, (NS == 1 ? HTR_MMA_CTAS : 2)) pa
 template <int K>
 int launch_packed_gemv_mma(const GemvParams& p, int grid, cudaStream_t stream);
 template <int K>
-int packed_gemv_mma_ctas_per_sm(int rows);
+int packed_gemv_mma_ctas_per_sm(int rows, int dtype);
+// one MMA set (and, beyond two rows, two planes per activation) when the results are rounded to bf16 anyway
+inline bool mma_one_set(int rows, int dtype) { return rows <= 2 || dtype == HTR_DTYPE_BF16; }
 
 }  // namespace htr

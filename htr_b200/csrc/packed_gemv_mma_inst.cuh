@@ -43,14 +43,15 @@ static int occupancy_mma_one() {
   return ctas;
 }
 
+// one MMA set serves two rows with four planes each, or four rows of 16-bit activations with two planes each
 template <>
 int launch_packed_gemv_mma<HTR_INST_K>(const GemvParams& p, int grid, cudaStream_t stream) {
-  return p.rows <= 2 ? launch_mma_one<HTR_INST_K, 1>(p, grid, stream) : launch_mma_one<HTR_INST_K, 2>(p, grid, stream);
+  return mma_one_set(p.rows, p.dtype) ? launch_mma_one<HTR_INST_K, 1>(p, grid, stream) : launch_mma_one<HTR_INST_K, 2>(p, grid, stream);
 }
 
 template <>
-int packed_gemv_mma_ctas_per_sm<HTR_INST_K>(int rows) {
-  return rows <= 2 ? occupancy_mma_one<HTR_INST_K, 1>() : occupancy_mma_one<HTR_INST_K, 2>();
+int packed_gemv_mma_ctas_per_sm<HTR_INST_K>(int rows, int dtype) {
+  return mma_one_set(rows, dtype) ? occupancy_mma_one<HTR_INST_K, 1>() : occupancy_mma_one<HTR_INST_K, 2>();
 }
 
 }  // namespace htr

@@ -209,9 +209,10 @@ int htr_codebook_f32(float* out, htr_stream_t stream);
 /* Launch-shape knobs of htr_linear for measurements (0 = library default): CTAs per SM of the GEMV grid. */
 void htr_set_gemv_ctas_per_sm(int ctas);
 /* Which kernel serves htr_linear and its variants for up to four activation rows: 0 = the CUDA-core GEMV, 1 = the tcgen05 GEMV
- * (hash words in tensor memory), 2 = the warp-MMA GEMV (hash words as mma.sync fragments), -1 = the default (environment
- * variable HTR_GEMV_TC, else the build default).  Workspace sizes must be queried under the same setting as the call that uses
- * them. */
+ * (hash words in tensor memory), 2 = the warp-MMA GEMV (hash words as mma.sync fragments), -1 = the default: environment
+ * variable HTR_GEMV_TC if set, else by measurement (one row, and three or four float32 or fp16 rows: CUDA-core GEMV; two rows, and
+ * three or four bf16 rows: warp-MMA GEMV).  Workspace sizes must be queried under the same setting as the call that
+ * uses them. */
 void htr_set_gemv_tc(int mode);
 /* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block);
