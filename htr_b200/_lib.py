@@ -17,7 +17,7 @@ INPUT_INDEPENDENT = 1
 
 EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
            "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_peers", "htr_linear_grouped", "htr_linear_grouped_workspace_bytes", "htr_linear_routed", "htr_linear_static", "htr_linear_padded", "htr_linear_fused", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_linear_gemm_last_cuda_error", "htr_dequant_w", "htr_viterbi", "htr_viterbi_workspace_bytes", "htr_viterbi_last_cuda_error", "htr_codebook_f32",
-           "htr_set_gemv_ctas_per_sm", "htr_linear_plan", "htr_gemv_tc_failures", "htr_gemv_tc_last_failure", "htr_set_gemv_tc", "htr_dec_add_rmsnorm", "htr_dec_rope_cache", "htr_dec_attention",
+           "htr_linear_plan", "htr_set_gemv_kernel", "htr_dec_add_rmsnorm", "htr_dec_rope_cache", "htr_dec_attention",
            "htr_dec_swiglu", "htr_dec_rope_attention")
 
 
@@ -45,7 +45,7 @@ def _load():
     lib.htr_linear_ex.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp, ctypes.c_uint]
     lib.htr_linear_peers.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, vp, sz, vp, ctypes.c_uint]
     lib.htr_linear_grouped.argtypes = [vp, i32, vp, i32, i32, i32, vp, vp, vp, vp, i32, vp, sz, vp]
-    lib.htr_linear_routed.argtypes = [vp, i32, i32, i64, vp, i32, vp, vp, vp, vp, i32, i32, i32, vp, i32, vp, sz, vp]
+    lib.htr_linear_routed.argtypes = [vp, i32, i32, i64, vp, i32, i32, vp, vp, vp, vp, i32, i32, i32, vp, i32, vp, sz, vp]
     lib.htr_linear_grouped_workspace_bytes.restype = sz
     lib.htr_linear_grouped_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.htr_linear_static.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp]
@@ -61,17 +61,13 @@ def _load():
     lib.htr_linear_gemm_error_offset.restype = sz
     lib.htr_dequant_w.argtypes = [vp, i32, i32, i32, vp, vp, vp, vp, i32, vp]
     lib.htr_dec_add_rmsnorm.argtypes = [vp, vp, vp, vp, i32, i32, ctypes.c_float, vp]
-    lib.htr_dec_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
-    lib.htr_dec_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.htr_dec_rope_cache.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
+    lib.htr_dec_attention.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]
     lib.htr_dec_swiglu.argtypes = [vp, vp, i32, i32, vp]
-    lib.htr_dec_rope_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp]
-    lib.htr_set_gemv_ctas_per_sm.restype = None
-    lib.htr_set_gemv_ctas_per_sm.argtypes = [i32]
+    lib.htr_dec_rope_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
     lib.htr_linear_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
-    lib.htr_gemv_tc_failures.argtypes = [ctypes.POINTER(i32)]
-    lib.htr_gemv_tc_last_failure.argtypes = [ctypes.POINTER(ctypes.c_uint)]
-    lib.htr_set_gemv_tc.restype = None
-    lib.htr_set_gemv_tc.argtypes = [i32]
+    lib.htr_set_gemv_kernel.restype = None
+    lib.htr_set_gemv_kernel.argtypes = [i32]
     return lib
 
 

@@ -4,7 +4,6 @@
 #include <mutex>
 
 #include "packed_gemv_mma.cuh"
-#include "packed_gemv_tc.cuh"
 
 namespace htr {
 int run_decode_raw(int K, const uint32_t* qw, int16_t* out, long long ntiles, cudaStream_t st);
@@ -12,12 +11,7 @@ int run_rht(const void* x, int dtype, int M, int n, const uint8_t* su, float* xt
 int run_dequant_w(int K, const uint32_t* qw, const __half* scales, const uint8_t* su, const uint8_t* sv, float cb, void* W,
                   int out_dtype, int mt, int nt, cudaStream_t st);
 
-#ifndef HTR_GEMV_TC_DEFAULT
-#define HTR_GEMV_TC_DEFAULT -1
-#endif
-
 static thread_local int t_last_cuda = 0;
-static int g_ctas_override = 0;
 
 static int cuda_fail(int e) {
   t_last_cuda = e;
@@ -54,37 +48,25 @@ static int gemv_ctas_per_sm(int K, int mt_rows) {
   return -1;
 }
 
-static int gemv_tc_ctas_per_sm(int K) {
+static int gemv_mma_config(int K, int rows, int* ctas, int* cap) {
   switch (K) {
-    case 2: return packed_gemv_tc_ctas_per_sm<2>();
-    case 3: return packed_gemv_tc_ctas_per_sm<3>();
-    case 4: return packed_gemv_tc_ctas_per_sm<4>();
-    case 5: return packed_gemv_tc_ctas_per_sm<5>();
-    case 6: return packed_gemv_tc_ctas_per_sm<6>();
-    case 8: return packed_gemv_tc_ctas_per_sm<8>();
+    case 2: return packed_gemv_mma_config<2>(rows, ctas, cap);
+    case 3: return packed_gemv_mma_config<3>(rows, ctas, cap);
+    case 4: return packed_gemv_mma_config<4>(rows, ctas, cap);
+    case 5: return packed_gemv_mma_config<5>(rows, ctas, cap);
+    case 6: return packed_gemv_mma_config<6>(rows, ctas, cap);
+    case 8: return packed_gemv_mma_config<8>(rows, ctas, cap);
   }
-  return -1;
+  return (int)cudaErrorInvalidValue;
 }
 
-static int gemv_mma_ctas_per_sm(int K, int rows, int dtype) {
-  switch (K) {
-    case 2: return packed_gemv_mma_ctas_per_sm<2>(rows, dtype);
-    case 3: return packed_gemv_mma_ctas_per_sm<3>(rows, dtype);
-    case 4: return packed_gemv_mma_ctas_per_sm<4>(rows, dtype);
-    case 5: return packed_gemv_mma_ctas_per_sm<5>(rows, dtype);
-    case 6: return packed_gemv_mma_ctas_per_sm<6>(rows, dtype);
-    case 8: return packed_gemv_mma_ctas_per_sm<8>(rows, dtype);
-  }
-  return -1;
-}
-
-// Which kernel serves single problems of up to four activation rows: 0 = CUDA-core GEMV, 1 = tcgen05 GEMV (A operand in tensor
-// memory), 2 = warp-MMA GEMV, -1 = by measurement (below).  HTR_GEMV_TC in the environment overrides the build default.
+// Which kernel serves single problems of up to four activation rows: 0 = CUDA-core GEMV, 1 = warp-MMA GEMV, -1 = by measurement
+// (gemv_kind below).  HTR_GEMV_KERNEL in the environment sets the default of the process.
 static int gemv_kind_default() {
   static const int kind = [] {
-    const char* v = std::getenv("HTR_GEMV_TC");
-    const int k = v ? std::atoi(v) : HTR_GEMV_TC_DEFAULT;
-    return k < -1 || k > 2 ? -1 : k;
+    const char* v = std::getenv("HTR_GEMV_KERNEL");
+    const int k = v ? std::atoi(v) : -1;
+    return k < -1 || k > 1 ? -1 : k;
   }();
   return kind;
 }
@@ -101,6 +83,7 @@ struct Plan {
   int grid, slots, rows_t, split;
   int units;
   int cg, rbs;
+  int wblocks;       // warp-MMA kernel: 128-column blocks of activations staged at a time
 };
 
 // device facts are cached per device; the occupancy of each instantiation is cached per (device, K, rows)
@@ -123,40 +106,37 @@ static int cached_occupancy(int dev, int K, int rows_t) {
   return slot;
 }
 
-static int cached_tc_occupancy(int dev, int K) {
-  static int cache[64][9] = {{0}};
+// warp-MMA kernel: CTAs per SM and the window cap, per (device, K, rows)
+static int cached_mma_config(int dev, int K, int rows, int* ctas, int* cap) {
+  struct Entry { int ctas, cap; };
+  static Entry cache[64][9][kMmaRows + 1] = {};
   static std::mutex mu;
-  if (dev < 0 || dev >= 64) return gemv_tc_ctas_per_sm(K);
+  if (dev < 0 || dev >= 64) return gemv_mma_config(K, rows, ctas, cap);
   std::lock_guard<std::mutex> lock(mu);
-  int& slot = cache[dev][K];
-  if (slot == 0) slot = gemv_tc_ctas_per_sm(K);
-  return slot;
+  Entry& slot = cache[dev][K][rows];
+  if (slot.ctas == 0) {
+    int c = 0, w = 0;
+    if (const int e = gemv_mma_config(K, rows, &c, &w)) return e;
+    slot.ctas = c;
+    slot.cap = w;
+  }
+  *ctas = slot.ctas;
+  *cap = slot.cap;
+  return 0;
 }
 
-// the tensor-core GEMV serves single problems of up to four activation rows
-static int cached_mma_occupancy(int dev, int K, int rows, int dtype) {
-  static int cache[64][9][2] = {{{0}}};
-  static std::mutex mu;
-  if (dev < 0 || dev >= 64) return gemv_mma_ctas_per_sm(K, rows, dtype);
-  std::lock_guard<std::mutex> lock(mu);
-  int& slot = cache[dev][K][mma_one_set(rows, dtype) ? 0 : 1];
-  if (slot == 0) slot = gemv_mma_ctas_per_sm(K, rows, dtype);
-  return slot;
-}
-
-static int g_tc_override = -1;                         // -1: environment / build default, else the kind
-// Measured policy (4096x12288 K4, bf16): one row 12.2 us on the CUDA-core kernel against 12.5 on the warp-MMA kernel; two rows 15.8
-// against 14.3 (one MMA set serves both); three and four rows of 16-bit activations 21.4 / 22.0 against 16.2 / 17.9 (two planes per
-// activation, one set); three and four float32 or fp16 rows need two sets of four planes and lose (22.1 against 25.6).
+static int g_kind_override = -1;                       // -1: environment default, else the kind
+// Measured policy (4096x12288 K4, bf16): one row is cheapest on the CUDA-core kernel -- an int8 mma.sync costs about as many issue
+// slots as the byte sums and multiply-adds it replaces, and its activation staging is heavier; from two rows on the MMA serves the
+// extra rows for free.  Three or four float32 / fp16 rows (which would need more planes than an MMA holds) and five to eight rows
+// stay on the CUDA-core kernel.
 static int gemv_kind(int M, int dtype = HTR_DTYPE_BF16) {
-  if (M > kTcRows) return 0;
-  const int kind = g_tc_override >= 0 ? g_tc_override : gemv_kind_default();
-  if (kind >= 0) return kind;
-  // (fp16 results carry 11 bits: there the two-plane form would double the error of the output rounding, so fp16 keeps four planes)
-  return M == 2 || (M > 2 && dtype == HTR_DTYPE_BF16) ? 2 : 0;
+  if (!mma_serves(M, dtype)) return 0;
+  const int kind = g_kind_override >= 0 ? g_kind_override : gemv_kind_default();
+  return kind >= 0 ? kind : (M >= 2 ? 1 : 0);
 }
 
-static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0, int dtype = HTR_DTYPE_BF16) {
+static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail((int)e);
@@ -164,8 +144,12 @@ static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0, int dt
   if (sms <= 0) return cuda_fail((int)cudaErrorInvalidDevice);
   Plan pl;
   pl.rows_t = template_rows(M);
-  int per_sm = kind == 1 ? cached_tc_occupancy(dev, K) : kind == 2 ? cached_mma_occupancy(dev, K, M, dtype)
-               : g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, pl.rows_t);
+  int per_sm = 0, window_cap = 0;
+  if (kind == 1) {
+    if (const int ce = cached_mma_config(dev, K, M, &per_sm, &window_cap)) return cuda_fail(ce);
+  } else {
+    per_sm = cached_occupancy(dev, K, pl.rows_t);
+  }
   if (per_sm <= 0) return cuda_fail((int)cudaErrorLaunchOutOfResources);
   pl.rbs = m / 128;
   pl.cg = n / 64;
@@ -174,18 +158,29 @@ static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0, int dt
   // Short ranges: give every row block the same number of CTAs so that none crosses a row block (a crossing costs
   // one extra publish + restage, which is only cheap when a CTA owns many units).  Otherwise: flat even ranges.
   const long long flat_grid = cap < pl.units ? cap : pl.units;
+  int longest;                                            // units of one row block that a CTA may own
   if (pl.rbs <= cap && pl.units / flat_grid < 24) {
     long long s = cap / pl.rbs;
     if (s > pl.cg) s = pl.cg;
     pl.split = (int)s;
     pl.grid = pl.rbs * pl.split;
     pl.slots = pl.split;
+    longest = (pl.cg + pl.split - 1) / pl.split;
   } else {
     pl.split = 0;
     pl.grid = (int)flat_grid;
     // a row block holds cg units and a CTA at least floor(U/G) of them
     const int per_cta = pl.units / pl.grid;
     pl.slots = (pl.cg + per_cta - 1) / per_cta + 1;
+    longest = per_cta + 1 < pl.cg ? per_cta + 1 : pl.cg;
+  }
+  pl.wblocks = 0;
+  if (kind == 1) {
+    // a run of L units touches at most L/2 + 1 blocks; the windows of a run are made equally long
+    int need = longest / 2 + 1;
+    if (need > pl.cg / 2) need = pl.cg / 2;
+    const int windows = (need + window_cap - 1) / window_cap;
+    pl.wblocks = (need + windows - 1) / windows;
   }
   *out = pl;
   return HTR_OK;
@@ -205,7 +200,7 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
                          int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags,
                          int prologue = 0, const void* norm_w = nullptr, float eps = 0.f, int residual = 0);
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
-                          const int64_t* route, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
+                          const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
                           void* workspace, size_t workspace_bytes, htr_stream_t stream);
 
@@ -228,8 +223,7 @@ const char* htr_status_string(int status) {
 int htr_last_cuda_error(void) { return t_last_cuda; }
 int htr_version(void) { return 100; }
 
-void htr_set_gemv_ctas_per_sm(int ctas) { g_ctas_override = ctas > 0 ? ctas : 0; }
-void htr_set_gemv_tc(int mode) { g_tc_override = mode < 0 || mode > 2 ? -1 : mode; }   // -1: back to the default
+void htr_set_gemv_kernel(int kind) { g_kind_override = kind < 0 || kind > 1 ? -1 : kind; }   // -1: back to the default
 
 int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
@@ -258,12 +252,10 @@ size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
   Plan pl;
   if (make_plan(M, m, n, K, &pl) != HTR_OK) return 0;
   size_t slots = (size_t)pl.slots;
-  for (int dtype = HTR_DTYPE_BF16; dtype <= HTR_DTYPE_F32; ++dtype) {   // any of the kernels may serve the call: size for all
-    const int kind = gemv_kind(M, dtype);
-    if (kind == 0) continue;
-    Plan tc;
-    if (make_plan(M, m, n, K, &tc, kind, dtype) != HTR_OK) return 0;
-    if ((size_t)tc.slots > slots) slots = (size_t)tc.slots;
+  if (M <= kMmaRows) {                                   // either kernel may serve the call: size for both
+    Plan mma;
+    if (make_plan(M, m, n, K, &mma, 1) != HTR_OK) return 0;
+    if ((size_t)mma.slots > slots) slots = (size_t)mma.slots;
   }
   return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * sizeof(float);
 }
@@ -336,7 +328,7 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   const int m = mt * 16, n = nt * 16;
   Plan pl;
   const int kind = gemv_kind(M, dtype);
-  const int rc = make_plan(M, m, n, K, &pl, kind, dtype);
+  const int rc = make_plan(M, m, n, K, &pl, kind);
   if (rc != HTR_OK) return rc;
   const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
@@ -358,10 +350,13 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.cg = pl.cg;
   p.units = pl.units;
   p.split = pl.split;
+  p.cg_quot = pl.split > 0 ? pl.cg / pl.split : 0;
+  p.cg_rem = pl.split > 0 ? pl.cg % pl.split : 0;
   p.independent = (flags & HTR_LINEAR_INPUT_INDEPENDENT) ? 1 : 0;
   p.n_in = n_in;
   p.m_out = m_out;
   p.g_route = nullptr;
+  p.g_table_rows = 0;
   p.g_xdiv = 1;
   p.g_xrow_bytes = 0;
   p.g_yrow_bytes = 0;
@@ -377,10 +372,11 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.peer_offset = peer_offset;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = i < npeer ? peer_y[i] : nullptr;
   p.slots = pl.slots;
+  p.wblocks = pl.wblocks;
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int e = 0;
-  if (kind == 2) {
+  if (kind == 1) {
     switch (K) {
       case 2: e = launch_packed_gemv_mma<2>(p, pl.grid, st); break;
       case 3: e = launch_packed_gemv_mma<3>(p, pl.grid, st); break;
@@ -388,17 +384,6 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
       case 5: e = launch_packed_gemv_mma<5>(p, pl.grid, st); break;
       case 6: e = launch_packed_gemv_mma<6>(p, pl.grid, st); break;
       case 8: e = launch_packed_gemv_mma<8>(p, pl.grid, st); break;
-    }
-    return e ? cuda_fail(e) : HTR_OK;
-  }
-  if (kind == 1) {
-    switch (K) {
-      case 2: e = launch_packed_gemv_tc<2>(p, pl.grid, st); break;
-      case 3: e = launch_packed_gemv_tc<3>(p, pl.grid, st); break;
-      case 4: e = launch_packed_gemv_tc<4>(p, pl.grid, st); break;
-      case 5: e = launch_packed_gemv_tc<5>(p, pl.grid, st); break;
-      case 6: e = launch_packed_gemv_tc<6>(p, pl.grid, st); break;
-      case 8: e = launch_packed_gemv_tc<8>(p, pl.grid, st); break;
     }
     return e ? cuda_fail(e) : HTR_OK;
   }
@@ -410,40 +395,6 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
     case 6: e = launch_packed_gemv<6>(p, pl.rows_t, pl.grid, st); break;
     case 8: e = launch_packed_gemv<8>(p, pl.rows_t, pl.grid, st); break;
   }
-  return e ? cuda_fail(e) : HTR_OK;
-}
-
-static int tc_failures(int* count, unsigned* last) {
-  int total = 0, one = 0, e = 0;
-  unsigned where = 0u, w = 0u;
-  if ((e = packed_gemv_tc_failures<2>(&one, &w))) return e;
-  total += one; if (one) where = w;
-  if ((e = packed_gemv_tc_failures<3>(&one, &w))) return e;
-  total += one; if (one) where = w;
-  if ((e = packed_gemv_tc_failures<4>(&one, &w))) return e;
-  total += one; if (one) where = w;
-  if ((e = packed_gemv_tc_failures<5>(&one, &w))) return e;
-  total += one; if (one) where = w;
-  if ((e = packed_gemv_tc_failures<6>(&one, &w))) return e;
-  total += one; if (one) where = w;
-  if ((e = packed_gemv_tc_failures<8>(&one, &w))) return e;
-  total += one; if (one) where = w;
-  *count = total;
-  *last = where;
-  return 0;
-}
-
-int htr_gemv_tc_failures(int* count) {
-  if (!count) return HTR_ERR_NULL;
-  unsigned where = 0u;
-  const int e = tc_failures(count, &where);
-  return e ? cuda_fail(e) : HTR_OK;
-}
-
-int htr_gemv_tc_last_failure(unsigned* where) {
-  if (!where) return HTR_ERR_NULL;
-  int count = 0;
-  const int e = tc_failures(&count, where);
   return e ? cuda_fail(e) : HTR_OK;
 }
 
@@ -459,26 +410,27 @@ int htr_linear_grouped(const void* const* x_list, int dtype, const void* const* 
                        const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, void* const* y_list,
                        int count, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
   if (count > 0 && (!x_list || !y_list)) return HTR_ERR_NULL;
-  return launch_grouped(x_list, y_list, nullptr, nullptr, 1, 0, nullptr, 0, dtype, qweight_list, mt, nt, K, scales_list, su_list, sv_list, count,
+  return launch_grouped(x_list, y_list, nullptr, nullptr, 1, 0, nullptr, count, 0, dtype, qweight_list, mt, nt, K, scales_list, su_list, sv_list, count,
                         workspace, workspace_bytes, stream);
 }
 
-int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count,
+int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count, int table_rows,
                       const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
                       const uint8_t* const* sv_table, int mt, int nt, int K, void* y, int prologue, void* workspace, size_t workspace_bytes,
                       htr_stream_t stream) {
   if (count > 0 && (!x || !y || !route)) return HTR_ERR_NULL;
-  if (x_div < 1 || x_row_stride < 0 || (prologue != HTR_PROLOGUE_NONE && prologue != HTR_PROLOGUE_SWIGLU)) return HTR_ERR_BAD_SHAPE;
+  if (x_div < 1 || x_row_stride < 0 || table_rows < 1 || (prologue != HTR_PROLOGUE_NONE && prologue != HTR_PROLOGUE_SWIGLU))
+    return HTR_ERR_BAD_SHAPE;
   if (prologue == HTR_PROLOGUE_SWIGLU && dtype != HTR_DTYPE_BF16) return HTR_ERR_BAD_DTYPE;
   if (count > 0 && (!aligned16(x) || !aligned16(y))) return HTR_ERR_ALIGNMENT;
-  return launch_grouped(nullptr, nullptr, x, y, x_div, x_row_stride, route, prologue, dtype, qweight_table, mt, nt, K, scales_table, su_table,
+  return launch_grouped(nullptr, nullptr, x, y, x_div, x_row_stride, route, table_rows, prologue, dtype, qweight_table, mt, nt, K, scales_table, su_table,
                         sv_table, count, workspace, workspace_bytes, stream);
 }
 
 // shared body of the grouped entry points: per-problem pointer lists (x_list / y_list), or a route into per-expert tables with the
 // activations and outputs as rows of two matrices
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
-                          const int64_t* route, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
+                          const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
                           void* workspace, size_t workspace_bytes, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
@@ -495,7 +447,7 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   int dev = 0;
   cudaGetDevice(&dev);
   const int sms = device_sms(dev);
-  const int per_sm = g_ctas_override > 0 ? g_ctas_override : cached_occupancy(dev, K, 1);
+  const int per_sm = cached_occupancy(dev, K, 1);
   const long long cap = (long long)sms * per_sm;
   const long long rbs = (long long)count * rbp;
   long long split = cap / rbs;
@@ -515,6 +467,8 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   p.cg = pl.cg;
   p.units = (int)(rbs * pl.cg);
   p.split = (int)split;
+  p.cg_quot = pl.cg / (int)split;
+  p.cg_rem = pl.cg % (int)split;
   p.slots = (int)split;
   p.independent = 0;
   p.cb = (float)codebook_scale();
@@ -527,12 +481,14 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   p.norm_w = nullptr;
   p.eps = 0.f;
   p.g_route = reinterpret_cast<const long long*>(route);
+  p.g_table_rows = table_rows;
   p.g_xdiv = x_div;
   const long long esz = dtype == HTR_DTYPE_F32 ? 4 : 2;
   p.g_xrow_bytes = (long long)x_row_stride * esz;
   p.g_yrow_bytes = (long long)m * esz;
   p.peer_offset = 0;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
+  p.wblocks = 0;
   p.group = count;
   p.rb_per_problem = rbp;
   p.g_x = x_list;

@@ -87,10 +87,14 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__nv_bfloat16* __restr
 // rotary embedding of q and k (interleaved pairs), k and v written into the cache rows pos[t].  grid (heads_q + 2*heads_kv, T), D/2 threads.
 __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ pos, const float* __restrict__ cosv,
                                   const float* __restrict__ sinv, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache,
-                                  __nv_bfloat16* __restrict__ v_cache, int hq, int hkv, int D) {
+                                  __nv_bfloat16* __restrict__ v_cache, int hq, int hkv, int D, int capacity, int* __restrict__ status) {
   pdl_enter();
   const int head = blockIdx.x, t = blockIdx.y, i = threadIdx.x;           // pair index i: elements 2i, 2i+1
   const long long p = pos[t];
+  if (p < 0 || p >= capacity) {                                           // a position outside the cache: nothing is read or written
+    if (status && i == 0 && head == 0) atomicOr(status, 1);
+    return;
+  }
   const size_t row = (size_t)t * (hq + 2 * hkv) * D;
   const __nv_bfloat162 in = *reinterpret_cast<const __nv_bfloat162*>(qkv + row + (size_t)head * D + 2 * i);
   if (head >= hq + hkv) {                                                 // v: plain copy into the cache
@@ -104,12 +108,13 @@ __global__ void rope_cache_kernel(const __nv_bfloat16* __restrict__ qkv, const l
   else *reinterpret_cast<__nv_bfloat162*>(k_cache + ((size_t)p * hkv + (head - hq)) * D + 2 * i) = r;
 }
 
-// out[t, head, :] = softmax(q . K[0..pos[t]] / sqrt(D)) V.  grid (heads_q, T), 128 threads, D == 128, positions <= HTR_DEC_MAX_LEN.
+// out[t, head, :] = softmax(q . K[0..pos[t]] / sqrt(D)) V.  grid (heads_q, T), 128 threads, D == 128, positions < min(capacity,
+// HTR_DEC_MAX_LEN); a row whose position lies outside gets zeros and sets the status word.
 // Scores: one thread per position (128 positions per pass, the 256-byte key row read as sixteen 16-byte loads);
 // values: one thread per dimension, eight positions in flight.
 __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                                                         const __nv_bfloat16* __restrict__ v_cache, const long long* __restrict__ pos,
-                                                        __nv_bfloat16* __restrict__ out, int hq, int hkv) {
+                                                        __nv_bfloat16* __restrict__ out, int hq, int hkv, int capacity, int* __restrict__ status) {
   constexpr int D = 128;
   __shared__ __align__(16) float sq[D];
   __shared__ float sc[HTR_DEC_MAX_LEN];
@@ -117,7 +122,13 @@ __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __r
   pdl_enter();
   const int head = blockIdx.x, t = blockIdx.y, tid = threadIdx.x;
   const int kvh = head / (hq / hkv);
-  const int len = (int)pos[t] + 1;
+  const long long pt = pos[t];
+  if (pt < 0 || pt >= capacity || pt >= HTR_DEC_MAX_LEN) {                // the whole CTA takes this branch: no barrier is skipped by a part of it
+    if (status && tid == 0 && head == 0) atomicOr(status, 2);
+    out[((size_t)t * hq + head) * D + tid] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int len = (int)pt + 1;
   sq[tid] = bf(q[((size_t)t * hq + head) * D + tid]) * 0.08838834764831845f;   // 1/sqrt(128)
   __syncthreads();
   float mx = -3.0e38f;
@@ -164,7 +175,8 @@ __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __r
 __global__ void __launch_bounds__(128) rope_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ pos,
                                                              const float* __restrict__ cosv, const float* __restrict__ sinv,
                                                              __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-                                                             __nv_bfloat16* __restrict__ out, int hq, int hkv) {
+                                                             __nv_bfloat16* __restrict__ out, int hq, int hkv, int capacity,
+                                                             int* __restrict__ status) {
   constexpr int D = 128;
   __shared__ __align__(16) float sq[D];
   __shared__ float sk[D], sv[D];
@@ -173,7 +185,13 @@ __global__ void __launch_bounds__(128) rope_attention_kernel(const __nv_bfloat16
   pdl_enter();
   const int head = blockIdx.x, tid = threadIdx.x;
   const int rep = hq / hkv, kvh = head / rep;
-  const int p = (int)pos[0], len = p + 1;
+  const long long p0 = pos[0];
+  if (p0 < 0 || p0 >= capacity || p0 >= HTR_DEC_MAX_LEN) {                // outside the cache: no cache row is touched, zeros come out
+    if (status && tid == 0 && head == 0) atomicOr(status, 4);
+    out[(size_t)head * D + tid] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int p = (int)p0, len = p + 1;
   {
     const int i = tid >> 1;                                               // pair (2i, 2i+1); even threads own the first element
     const float c = cosv[(size_t)p * (D / 2) + i], s = sinv[(size_t)p * (D / 2) + i];
@@ -276,36 +294,36 @@ int htr_dec_add_rmsnorm(void* resid, const void* delta, const void* weight, void
 }
 
 int htr_dec_rope_cache(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* q_out, void* k_cache, void* v_cache,
-                       int rows, int q_heads, int kv_heads, int head_dim, htr_stream_t stream) {
+                       int rows, int q_heads, int kv_heads, int head_dim, int capacity, int* status, htr_stream_t stream) {
   if (rows <= 0) return HTR_OK;
   if (!qkv || !pos || !cosv || !sinv || !q_out || !k_cache || !v_cache) return HTR_ERR_NULL;
-  if (head_dim <= 0 || head_dim % 2 || head_dim > 2048 || q_heads <= 0 || kv_heads <= 0) return HTR_ERR_BAD_SHAPE;
+  if (head_dim <= 0 || head_dim % 2 || head_dim > 2048 || q_heads <= 0 || kv_heads <= 0 || capacity <= 0) return HTR_ERR_BAD_SHAPE;
   const int e = launch_pdl(rope_cache_kernel, dim3(q_heads + 2 * kv_heads, rows), dim3(head_dim / 2), static_cast<cudaStream_t>(stream),
                            static_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const long long*>(pos), cosv, sinv,
                            static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), q_heads,
-                           kv_heads, head_dim);
+                           kv_heads, head_dim, capacity, status);
   return e ? HTR_ERR_CUDA : HTR_OK;
 }
 
 int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int rows, int q_heads,
-                      int kv_heads, int head_dim, htr_stream_t stream) {
+                      int kv_heads, int head_dim, int capacity, int* status, htr_stream_t stream) {
   if (rows <= 0) return HTR_OK;
   if (!q || !k_cache || !v_cache || !pos || !out) return HTR_ERR_NULL;
-  if (head_dim != 128 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return HTR_ERR_BAD_SHAPE;
+  if (head_dim != 128 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || capacity <= 0) return HTR_ERR_BAD_SHAPE;
   const int e = launch_pdl(attention_kernel, dim3(q_heads, rows), dim3(128), static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(q),
                            static_cast<const __nv_bfloat16*>(k_cache), static_cast<const __nv_bfloat16*>(v_cache),
-                           reinterpret_cast<const long long*>(pos), static_cast<__nv_bfloat16*>(out), q_heads, kv_heads);
+                           reinterpret_cast<const long long*>(pos), static_cast<__nv_bfloat16*>(out), q_heads, kv_heads, capacity, status);
   return e ? HTR_ERR_CUDA : HTR_OK;
 }
 
 int htr_dec_rope_attention(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* k_cache, void* v_cache, void* out,
-                           int q_heads, int kv_heads, int head_dim, htr_stream_t stream) {
+                           int q_heads, int kv_heads, int head_dim, int capacity, int* status, htr_stream_t stream) {
   if (!qkv || !pos || !cosv || !sinv || !k_cache || !v_cache || !out) return HTR_ERR_NULL;
-  if (head_dim != 128 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads) return HTR_ERR_BAD_SHAPE;
+  if (head_dim != 128 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads || capacity <= 0) return HTR_ERR_BAD_SHAPE;
   const int e = launch_pdl(rope_attention_kernel, dim3(q_heads), dim3(128), static_cast<cudaStream_t>(stream),
                            static_cast<const __nv_bfloat16*>(qkv), reinterpret_cast<const long long*>(pos), cosv, sinv,
                            static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), static_cast<__nv_bfloat16*>(out), q_heads,
-                           kv_heads);
+                           kv_heads, capacity, status);
   return e ? HTR_ERR_CUDA : HTR_OK;
 }
 

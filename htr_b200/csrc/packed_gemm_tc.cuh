@@ -184,21 +184,6 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-#ifdef HTR_GEMM_TRACE
-// timeline probe for experiments: per-CTA %globaltimer stamps, compiled only on request
-static __device__ unsigned long long htr_gemm_trace_buf[512 * 128];
-__device__ __forceinline__ void gemm_stamp(int slot) {
-  if (blockIdx.x < 512 && slot < 128) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    htr_gemm_trace_buf[blockIdx.x * 128 + slot] = t;
-  }
-}
-#define HTR_GTRACE(cond, slot) do { if (cond) gemm_stamp(slot); } while (0)
-#else
-#define HTR_GTRACE(cond, slot)
-#endif
-
 // dynamic shared memory: stages {A tile, B tile}, then the packed-word rings of the decode warps -- later reused for
 // the [np][128] float result
 __host__ __device__ inline int gemm_stage_bytes(int ncols) { return kDecodeGroups * (kATileBytes + ncols * 128); }   // one pair
@@ -222,7 +207,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  HTR_GTRACE(tid == 0, 0);
   const int np = p.np, ncols = p.planes * np;               // accumulator columns: hi plane, then lo plane if present
   const int nt = p.nt, m = p.mt * 16, HB = p.hb, NS = p.stages;
   const int rb = blockIdx.x / p.split, part_id = blockIdx.x - rb * p.split;
@@ -286,7 +270,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
       asm volatile("cp.async.wait_group %0;" ::"n"(R - 2) : "memory");   // this chunk's words have landed (own copies) ...
       __syncwarp();                                                       // ... and those of the other lanes; slot of the previous chunk is free
       prefetch(c + kDecodeGroups * (R - 1), slot == 0 ? R - 1 : slot - 1);
-      HTR_GTRACE(tid == 0 && c < 20, 8 + 3 * (c >> 1));
       uint32_t V[K + 1];
       {
         const uint32_t* tile = reinterpret_cast<const uint32_t*>(ring + slot * kStripBytes) + tc * (8 * K);
@@ -311,7 +294,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
       }
       // the MMAs that read this ring slot (NS pairs ago) must have retired
       if (use > 0 && !__all_sync(kFullWarp, mbar_wait(smem_u32(&s_freed[st_idx]), (use - 1u) & 1u, &s_fail))) { ok = false; break; }
-      HTR_GTRACE(tid == 0 && c < 20, 9 + 3 * (c >> 1));
       unsigned char* dst0 = stage0 + st_idx * stage_bytes + group * kATileBytes + a_off;
       // 32 codebook integers of this lane unit as fp16 (1024 + bytesum): rows 2q and 2q+1 of the strip, 16 k each
       uint32_t st[32];
@@ -343,8 +325,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&s_afull[st_idx]));
-      HTR_GTRACE(tid == 0 && c < 20, 10 + 3 * (c >> 1));
-      HTR_GTRACE(lane == 0 && (c == 8 || c == 9), 40 + warp);
       if (++slot == R) slot = 0;
       if (++st_idx == NS) { st_idx = 0; ++use; }
     }
@@ -367,7 +347,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
           const uint32_t bar = smem_u32(&s_bfull[s]);
           mbar_expect_tx(bar, pair_b_bytes);
           bulk_load(stage0_addr + s * stage_bytes + kDecodeGroups * kATileBytes, bsrc + (size_t)pr * pair_b_bytes, pair_b_bytes, bar);
-          HTR_GTRACE(pr < 24, 100 + pr);
           ++issued;
           if (++s == NS) { s = 0; ++use; }
         }
@@ -386,9 +365,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
       bool ok = true;
       for (int pr = 0; pr < chunks / kDecodeGroups; ++pr) {
         if (!mbar_wait(smem_u32(&s_afull[s]), ph, &s_fail)) { ok = false; break; }
-        HTR_GTRACE(pr < 18, 64 + 2 * pr);
         if (!mbar_wait(smem_u32(&s_bfull[s]), ph, &s_fail)) { ok = false; break; }
-        HTR_GTRACE(pr < 18, 65 + 2 * pr);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_addr = stage0_addr + s * stage_bytes, b_addr = a_addr + kDecodeGroups * kATileBytes;
 #pragma unroll
@@ -412,7 +389,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
 
   // ---- all MMAs of this CTA done?
   if (!mbar_wait(smem_u32(&s_done), 0u, &s_fail)) s_fail = 1;
-  HTR_GTRACE(tid == 0, 2);
   asm volatile("griddepcontrol.wait;" ::: "memory");         // row sums / scales of the activations, scratch of earlier launches
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   __syncthreads();
@@ -442,7 +418,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  HTR_GTRACE(tid == 0, 3);
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
 
   if (p.cluster) {
@@ -495,7 +470,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
     }
     __syncthreads();
     finish = (s_arrival == contributors - 1);
-    HTR_GTRACE(tid == 0, 4);
     if (finish) {
       const float4* slot0 = reinterpret_cast<const float4*>(p.part + (size_t)rb * contributors * ((size_t)np * 128));
       for (int e = tid; e < np * 32; e += kGemmThreads) {
@@ -518,7 +492,6 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
   const unsigned sv_bits = sign_nibble(p.sv, rb * 32 + lane);
   float4 bias4 = make_float4(0.f, 0.f, 0.f, 0.f);
   if (p.bias) bias4 = load_quad(p.bias, row0, p.dtype);
-  HTR_GTRACE(tid == 0, 5);
   for (int j = warp; j < p.rows; j += kGemmWarps) {
     float xs = 0.f;
     for (int y = 0; y < p.xsum_slices; ++y) xs += p.xsum[j * p.xsum_slices + y];   // fixed order: results do not depend on scheduling

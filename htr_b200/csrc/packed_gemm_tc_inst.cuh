@@ -55,14 +55,3 @@ int launch_packed_gemm_tc<HTR_INST_K>(const GemmParams& p, int grid, cudaStream_
 
 }  // namespace htr
 
-#ifdef HTR_GEMM_TRACE
-#if HTR_INST_K == 4
-extern "C" int htr_gemm_trace_read(unsigned long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, htr::htr_gemm_trace_buf, sizeof(unsigned long long) * n);
-}
-extern "C" int htr_gemm_trace_clear() {
-  static unsigned long long zeros[512 * 128];
-  return (int)cudaMemcpyToSymbol(htr::htr_gemm_trace_buf, zeros, sizeof(zeros));
-}
-#endif
-#endif

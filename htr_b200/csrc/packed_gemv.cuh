@@ -19,9 +19,9 @@
 // touches the workspace or the output.
 //
 // Inside a CTA (256 threads): warp = (half h of the row block: strips 4h..4h+3) x (tile column c of the
-// unit); lane = (strip g, row pair q).  The packed words travel global -> shared memory through a ring of
-// kRing slots per warp, kRing - 1 of them in flight (16-byte cp.async, several units in flight per warp, no
-// registers held while they fly); a lane then reads its K words and the history word, rebuilds 32
+// unit); lane = (strip g, row pair q).  A loop trip covers one 128-column block (two units).  The packed words
+// travel global -> shared memory through a ring of trip-sized slots per warp, all but one of them in flight
+// (16-byte cp.async, no registers held while they fly); a lane then reads its K words and the history word, rebuilds 32
 // codebook integers in registers and multiplies them with the transformed activations, which all lanes of
 // the warp read from shared memory at the same address (broadcast).
 //
@@ -30,18 +30,9 @@
 // to float step uses the exact 1.5*2^23 bit trick with packed adds and FMAs (half the issue slots of
 // scalar ones), and part of the byte sums are moved to the shift/logic pipe (see unit_fma).
 #pragma once
-#include "htr_codec.cuh"
+#include <type_traits>
 
-// build-time tuning knobs (defaults are the measured best)
-#ifndef HTR_GEMV_ALU4
-#define HTR_GEMV_ALU4 3
-#endif
-#ifndef HTR_GEMV_UNROLL
-#define HTR_GEMV_UNROLL 1
-#endif
-#ifndef HTR_GEMV_RING
-#define HTR_GEMV_RING 5
-#endif
+#include "htr_codec.cuh"
 
 #include "htr_common.cuh"
 
@@ -51,9 +42,6 @@ constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kStageBlocks = 8;                  // 128-column blocks of activations staged at a time
 constexpr int kStageCols = kStageBlocks * 128;   // 1024 activations per row
-constexpr int kLoopUnroll = HTR_GEMV_UNROLL;                   // unit loop unrolling
-constexpr int kRing = HTR_GEMV_RING;                         // ring slots per warp; kRing - 1 units are in flight
-constexpr int kDepth = kRing - 1;
 constexpr int kCounterBytes = 1 << 16;           // arrival counters at the start of the workspace (16384 row blocks)
 
 struct GemvParams {
@@ -71,8 +59,10 @@ struct GemvParams {
   int dtype;        // element type of x, y, bias
   int cg;           // column groups per row block (nt / 4)
   int units;        // row blocks * cg
-  int split;        // > 0: every row block is shared by exactly `split` CTAs (grid = row blocks * split); 0: flat unit ranges
+  int split;        // > 0: every row block is shared by exactly `split` CTAs (grid = (split, row blocks)); 0: flat unit ranges
+  int cg_quot, cg_rem;   // split form: cg / split and cg % split (the first cg_rem parts of a row block hold one unit more)
   int slots;        // partial slots per row block
+  int wblocks;      // warp-MMA kernel only: 128-column blocks of activations staged at a time
   int independent;  // 1: x, bias and y are untouched by the preceding kernel of the stream (wait only before publishing)
   int n_in;         // columns present in x (row stride of x); columns n_in .. n-1 of the stored weight see zeros
   int m_out;        // rows written to y (row stride of y, length of bias); rows m_out .. m-1 of the stored weight are dropped
@@ -102,6 +92,7 @@ struct GemvParams {
   // Routed form: g_route[prob] = index into the four tables above (e.g. the expert of a (token, slot) pair); activations are
   // row prob / g_xdiv of the matrix at x (g_xrow_bytes apart), outputs row prob of the matrix at y (g_yrow_bytes apart).
   const long long* g_route;
+  int g_table_rows;  // rows of the four tables: a route entry outside [0, g_table_rows) skips its problem like a null weight pointer
   int g_xdiv;
   long long g_xrow_bytes, g_yrow_bytes;
 };
@@ -133,9 +124,6 @@ __device__ __forceinline__ float4 fused_x(const GemvParams& p, const void* x, in
 // owner CTA of unit x when CTA b starts at floor(b*U/G)
 __device__ __host__ inline int unit_owner(long long x, long long G, long long U) { return (int)(((x + 1) * G - 1) / U); }
 
-// dynamic shared memory of one CTA: staged activations (reused for the reductions) + the copy ring
-template <int K, int MT>
-constexpr int gemv_smem_bytes() { return MT * kStageCols * 4 + kRing * kGemvWarps * 4 * (32 * K); }
 
 __device__ __forceinline__ void async_copy16(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
@@ -188,8 +176,8 @@ __device__ __forceinline__ constexpr int staged_col_inv(int pos) {
 //
 // Pipe balance (measured on B200 with issue-rate probes): the hash multiply-add, the byte dot product and
 // the packed float ops share one half-rate pipe, the shifts/masks and the byte-wise |a-b| sum share another.
-// ALU4 of every 4 byte sums therefore go through the |a-b| form so that both pipes fill up together.
-template <int K, int MT, int ALU4 = HTR_GEMV_ALU4>
+// Three of every four byte sums therefore go through the |a-b| form so that both pipes fill up together.
+template <int K, int MT, int ALU4 = 3>
 __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float* __restrict__ xs, float2 (&acc)[MT][2]) {
   uint32_t s[32];
   unit_states<K>(V, s);
@@ -206,11 +194,7 @@ __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float
       for (int rr = 0; rr < 2; ++rr) {
         const uint32_t b0 = (2 * half + 2 * rr) % 4 < ALU4 ? code_magic_bits_alu(s[rr * 16 + c0]) : code_magic_bits(s[rr * 16 + c0]);
         const uint32_t b1 = (2 * half + 2 * rr + 1) % 4 < ALU4 ? code_magic_bits_alu(s[rr * 16 + c1]) : code_magic_bits(s[rr * 16 + c1]);
-#ifdef HTR_GEMV_SCALAR_UNBIAS
-        const float2 w = make_float2(__uint_as_float(b0) - kMagic, __uint_as_float(b1) - kMagic);
-#else
         const float2 w = __fadd2_rn(make_float2(__uint_as_float(b0), __uint_as_float(b1)), unbias);
-#endif
 #pragma unroll
         for (int r = 0; r < MT; ++r) {
           const float2 xp = half ? make_float2(xv[r].z, xv[r].w) : make_float2(xv[r].x, xv[r].y);
@@ -221,49 +205,65 @@ __device__ __forceinline__ void unit_fma(const uint32_t (&V)[K + 1], const float
   }
 }
 
-#ifdef HTR_GEMV_TRACE
-// timeline probe for experiments: per-CTA %globaltimer stamps, compiled only on request
-static __device__ unsigned long long htr_trace_buf[2048 * 8];
-__device__ __forceinline__ void trace_stamp(int slot) {
-  if (threadIdx.x == 0 && blockIdx.x < 2048) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    htr_trace_buf[blockIdx.x * 8 + slot] = t;
-  }
+// 16-byte asynchronous copy global -> shared when `on` is positive; both addresses carry a compile-time offset inside the instruction
+template <int OFF>
+__device__ __forceinline__ void async_copy16_at_if(uint32_t smem_addr, const void* gptr, int on) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.gt.s32 p, %2, 0;\n\t@p cp.async.cg.shared.global [%0+%3], [%1+%3], 16;\n\t}" ::"r"(smem_addr),
+      "l"(gptr), "r"(on), "n"(OFF)
+      : "memory");
 }
-#define HTR_TRACE(slot) trace_stamp(slot)
-#else
-#define HTR_TRACE(slot)
-#endif
+// the copies of one lane for one trip: both units of a 128-column block, chunk q + 8 j of its strip's tile in either unit
+template <int K, int U, int J>
+struct GemvTripCopies {
+  static __device__ __forceinline__ void run(uint32_t dst, const void* src, int on, int on_tail) {
+    constexpr int kChunks = 2 * K, kOff = U * 4 * (32 * K) + J * 128;
+    async_copy16_at_if<kOff>(dst, src, 8 * J + 8 <= kChunks ? on : on_tail);
+    if constexpr (8 * J + 8 < kChunks) GemvTripCopies<K, U, J + 1>::run(dst, src, on, on_tail);
+    else if constexpr (U == 0) GemvTripCopies<K, 1, 0>::run(dst, src, on, on_tail);
+  }
+};
+
+// ring stages (one trip = one 128-column block = two units of every warp each); one less is in flight
+template <int K>
+struct GemvStages {
+  static constexpr int value = K <= 3 ? 4 : 3;
+};
+template <int K, int MT>
+constexpr int gemv_smem_bytes() { return MT * kStageCols * 4 + GemvStages<K>::value * kGemvWarps * 8 * (32 * K); }
 
 template <int K, int MT>
 __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1)) packed_gemv_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   float* smem = reinterpret_cast<float*>(dyn_smem);                               // [MT][kStageCols], later reductions
-  uint32_t* ring = reinterpret_cast<uint32_t*>(dyn_smem + MT * kStageCols * 4);   // [kRing][warps][4 tiles][8K]
+  uint32_t* ring = reinterpret_cast<uint32_t*>(dyn_smem + MT * kStageCols * 4);   // [stage][warp][unit of the trip][4 strips][8K]
   __shared__ int s_arrival;
 
-  HTR_TRACE(0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int h = warp & 1, c = warp >> 1, g = lane >> 3, q = lane & 7;
   const int U = p.units, G = gridDim.x, CG = p.cg, nt = p.nt, n = nt * 16, m = p.mt * 16;
-  int u_begin, u_end;
+  // split form: grid (split, row blocks), the parts of a row block differ by at most one unit; flat form: even unit ranges
+  int u_begin, u_end, slot_index;
   if (p.split > 0) {
-    const int brb = blockIdx.x / p.split, part = blockIdx.x - brb * p.split;
-    u_begin = brb * CG + part * CG / p.split;
-    u_end = brb * CG + (part + 1) * CG / p.split;
+    const int part = blockIdx.x, base = blockIdx.y * CG;
+    u_begin = base + part * p.cg_quot + min(part, p.cg_rem);
+    u_end = u_begin + p.cg_quot + (part < p.cg_rem ? 1 : 0);
+    slot_index = part;
   } else {
     u_begin = (int)((long long)blockIdx.x * U / G);
     u_end = (int)(((long long)blockIdx.x + 1) * U / G);
+    slot_index = 0;                                     // found per row block below
   }
   constexpr int kTileWords = 8 * K, kTileBytes = 32 * K, kTileChunks = 2 * K;    // 16-byte chunks per tile
-  constexpr int kStageBytes = kGemvWarps * 4 * kTileBytes;
+  constexpr int kStages = GemvStages<K>::value, kDepth = kStages - 1;
+  constexpr int kStageBytes = kGemvWarps * 8 * kTileBytes;
 
-  // ring slot of (this warp, strip g): a lane group of 8 copies and reads its own tile
-  const uint32_t* my_ring = ring + (warp * 4 + g) * kTileWords;
+  // ring slot of (this warp, strip g): a lane group of 8 copies and reads its own tile of either unit
+  const uint32_t* my_ring = ring + (warp * 8 + g) * kTileWords;
   const uint32_t ring_dst = (uint32_t)__cvta_generic_to_shared(my_ring) + q * 16;
 
-  int rb = u_begin / CG, cgi = u_begin - rb * CG;
+  int rb = p.split > 0 ? (int)blockIdx.y : u_begin / CG;
+  int cgi = u_begin - rb * CG;
 
   // tensors of this CTA's problem (grouped form: one row block per CTA, so they never change inside a launch)
   const void* x_ptr = p.x;
@@ -278,6 +278,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     const int prob = rb / p.rb_per_problem;
     rb_base = prob * p.rb_per_problem;
     const long long entry = p.g_route ? p.g_route[prob] : prob;      // which row of the pointer tables
+    if (entry < 0 || entry >= p.g_table_rows) return;               // a route that points outside the tables: skipped, like a null weight
     qw_ptr = p.g_qw[entry];
     if (qw_ptr == nullptr) return;                                  // a problem this rank does not own (expert parallelism): nothing to do
     scales_ptr = p.g_scales[entry];
@@ -292,29 +293,25 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     }
   }
 
-  // prefetch cursor: runs kRing units ahead of the consumer along the same unit sequence.  Offsets are kept in
-  // 16-byte units relative to this lane's first chunk, so the bookkeeping is 32-bit.
-  const char* lane_base = reinterpret_cast<const char*>(qw_ptr) + ((size_t)((rb - rb_base) * 8 + 4 * h + g) * nt + (size_t)(4 * cgi + c)) * kTileBytes + q * 16;
-  constexpr int kStep16 = 4 * kTileBytes / 16;                    // next column group: four tiles further along the strip
-  const int wrap_extra16 = (7 * nt + 4) * (kTileBytes / 16) - kStep16;   // ... or the first column group of the next row block
-  int pf_off16 = 0, pf_left = u_end - u_begin, pf_in_rb = CG - cgi;
+  // Prefetch cursor of the current row block.  A trip brings the whole 128-column block (eight tiles of every strip) even where
+  // one of its two units belongs to the neighbouring CTA: only the first and the last block of a range can be such a block.
+  // The cursor never crosses a row block: at the end of one the ring runs empty and is primed again.
+  const int on_tail = (q + 8 * ((kTileChunks - 1) / 8) < kTileChunks) ? -1 : 0;   // all ones where this lane owns a chunk of the last copy
+  const char* pf_src = nullptr;
+  int pf_left = 0;                                      // trips of the row block that remain to be fetched
   auto issue = [&](int stage_bytes) {
-    // branch-free: past the end of the range the copies are predicated off and the cursor runs on harmlessly
-    const int on = pf_left > 0;
-    const char* src = lane_base + (size_t)(unsigned)pf_off16 * 16;
-#pragma unroll
-    for (int j = 0; j < (kTileChunks + 7) / 8; ++j) {
-      if (8 * j + 8 <= kTileChunks) async_copy16_if(ring_dst + stage_bytes + j * 128, src + j * 128, on);
-      else async_copy16_if(ring_dst + stage_bytes + j * 128, src + j * 128, on && (q + 8 * j < kTileChunks));
-    }
+    // no branches: past the end of the row block's range the copies are predicated off and the cursor runs on harmlessly
+    GemvTripCopies<K, 0, 0>::run(ring_dst + stage_bytes, pf_src, pf_left, pf_left & on_tail);
     --pf_left;
-    pf_off16 += kStep16;
-    if (--pf_in_rb == 0) {
-      pf_off16 += wrap_extra16;
-      pf_in_rb = CG;
-    }
+    pf_src += 8 * kTileBytes;
     async_commit();
   };
+  auto open_row_block = [&](int rb_, int cgi_, int units_left) {
+    const int stop = min(CG, cgi_ + units_left);
+    pf_left = ((stop + 1) >> 1) - (cgi_ >> 1);
+    pf_src = reinterpret_cast<const char*>(qw_ptr) + ((size_t)((rb_ - rb_base) * 8 + 4 * h + g) * nt + (size_t)(8 * (cgi_ >> 1) + c)) * kTileBytes + q * 16;
+  };
+  open_row_block(rb, cgi, u_end - u_begin);
   issue(0);
   // everything above touched only the weights; what follows reads activations and writes shared state
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -357,26 +354,26 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
 #pragma unroll
   for (int r = 0; r < MT; ++r) acc[r][0] = acc[r][1] = make_float2(0.f, 0.f);
 
-  int stage_bytes = 0, refill_bytes = (kRing - 1) * kStageBytes;
+  int stage_bytes = 0, refill_bytes = (kStages - 1) * kStageBytes;
   int u = u_begin;
   while (u < u_end) {
-    // ---- segment: units [u, seg_end) lie in row block rb and inside one staged window of activations
+    // ---- segment: units [cgi, seg_cg_end) lie in row block rb and inside one staged window of activations
     const int hb0 = cgi >> 1;                                       // first 128-column block needed
     const int cg_stop = min(CG, cgi + (u_end - u));                 // this CTA's last column group in rb, exclusive
     const int hb1 = min(hb0 + kStageBlocks, (cg_stop + 1) >> 1);
     const int seg_cg_end = min(cg_stop, hb1 * 2);
     __syncthreads();                                                // the previous users of the staging buffer are done
-    const int items = MT * (hb1 - hb0);
+    const int nblk = hb1 - hb0, items = MT * nblk;
     float4 xv_first = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (warp < items && warp / (hb1 - hb0) < p.rows)                // the first item's loads go out before the copy burst
-      xv_first = fused_x(p, x_ptr, warp / (hb1 - hb0), (hb0 + warp % (hb1 - hb0)) * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[warp / (hb1 - hb0)] : 1.f);
+    if (warp < items && warp / nblk < p.rows)                       // the first item's loads go out before the copy burst
+      xv_first = fused_x(p, x_ptr, warp / nblk, (hb0 + warp % nblk) * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[warp / nblk] : 1.f);
     if (!ring_primed) {
 #pragma unroll
       for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
       ring_primed = true;
     }
     for (int item = warp; item < items; item += kGemvWarps) {
-      const int r = item / (hb1 - hb0), hb = hb0 + item % (hb1 - hb0);
+      const int r = item / nblk, hb = hb0 + item % nblk;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (r < p.rows) {
         const float4 xv = item == warp ? xv_first : fused_x(p, x_ptr, r, hb * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[r] : 1.f);
@@ -389,31 +386,42 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       for (int k = 0; k < 4; ++k) dst[staged_col<K>(4 * (lane & 3) + k)] = v[k] * kInvSqrt128;
     }
     __syncthreads();
-    HTR_TRACE(1);
 
-    const float* xs = smem + (4 * cgi + c - hb0 * 8) * 16;
-    const int seg_units = seg_cg_end - cgi;
-#pragma unroll kLoopUnroll
-    for (int i = 0; i < seg_units; ++i) {
-      uint32_t V[K + 1];
-      async_wait<kDepth - 1>();                      // the oldest copy group (this unit) has landed
+    // ---- the trips of the window.  A trip: wait for its slot, refill the slot consumed one trip ago, decode FIRST and / or SECOND
+    // unit of the block.  Only the first and the last trip of the CTA's range can hold a foreign unit (never both in one trip:
+    // such a range would be empty); they are peeled off the steady loop, which has no conditional code.
+    const float* xs = smem + c * 16;
+    auto trip = [&](auto first, auto second) {
+      async_wait<kDepth - 1>();                      // the oldest copy group (this trip) has landed
       __syncwarp();                                  // ... for every lane; and every lane is done with the previous slot
-#ifdef HTR_GEMV_TRACE
-      if (u + i == u_begin) HTR_TRACE(2);
-#endif
-      read_unit_words<K>(reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_ring) + stage_bytes), q, V);
-      issue(refill_bytes);                           // refill the slot that was consumed one unit ago (or never used yet)
+      const uint32_t* tiles = reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_ring) + stage_bytes);
+      issue(refill_bytes);                           // refill the slot that was consumed one trip ago (or never used yet)
       refill_bytes = stage_bytes;
-      stage_bytes = (stage_bytes + kStageBytes == kRing * kStageBytes) ? 0 : stage_bytes + kStageBytes;
-      unit_fma<K, MT>(V, xs, acc);
-      xs += 64;
-    }
-    u += seg_units;
-    cgi += seg_units;
+      stage_bytes = (stage_bytes + kStageBytes == kStages * kStageBytes) ? 0 : stage_bytes + kStageBytes;
+      if constexpr (decltype(first)::value) {
+        uint32_t V[K + 1];
+        read_unit_words<K>(tiles, q, V);
+        unit_fma<K, MT>(V, xs, acc);
+      }
+      if constexpr (decltype(second)::value) {
+        uint32_t V[K + 1];
+        read_unit_words<K>(tiles + 4 * kTileWords, q, V);
+        unit_fma<K, MT>(V, xs + 64, acc);
+      }
+      xs += 128;
+    };
+    const int trips = ((seg_cg_end + 1) >> 1) - hb0;
+    const bool head = (cgi & 1) != 0, tail = (seg_cg_end & 1) != 0;   // (windows end on block boundaries except at the end of the range)
+    const int full = trips - (head ? 1 : 0) - (tail ? 1 : 0);
+    if (head) trip(std::false_type{}, std::true_type{});
+#pragma unroll 1
+    for (int t = 0; t < full; ++t) trip(std::true_type{}, std::true_type{});
+    if (tail) trip(std::true_type{}, std::false_type{});
+    u += seg_cg_end - cgi;
+    cgi = seg_cg_end;
     if (cgi < CG && u < u_end) continue;              // same row block, next staged window
 
     // ---- this CTA's contribution to row block rb is complete: reduce the four column warps
-    HTR_TRACE(3);
     __syncthreads();                                   // everyone is done reading the staged activations
     float* red = smem;                                  // [4][MT][128]
 #pragma unroll
@@ -425,13 +433,13 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       }
     __syncthreads();
 
-    int first, contributors;
+    int contributors;
     if (p.split > 0) {
-      first = rb * p.split;
       contributors = p.split;
     } else {
-      first = unit_owner((long long)rb * CG, G, U);
+      const int first = unit_owner((long long)rb * CG, G, U);
       contributors = unit_owner((long long)(rb + 1) * CG - 1, G, U) - first + 1;
+      slot_index = blockIdx.x - first;
     }
     float* ytil = smem + 4 * MT * 128;                  // [MT][128], disjoint from red (MT*kStageCols >= 5*MT*128)
     // operands of the epilogue are fetched now so that their latency hides behind the arrival handshake
@@ -450,17 +458,15 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     }
     bool finish = true;
     if (contributors > 1) {
-      float* mine = p.part + ((size_t)rb * p.slots + (blockIdx.x - first)) * (MT * 128);
+      float* mine = p.part + ((size_t)rb * p.slots + slot_index) * (MT * 128);
       for (int e = tid; e < MT * 128; e += kGemvThreads)
         __stcg(mine + e, red[e] + red[MT * 128 + e] + red[2 * MT * 128 + e] + red[3 * MT * 128 + e]);
       __syncthreads();
       if (tid == 0) {
         __threadfence();                               // the partials of the whole CTA (ordered by the barrier) before the arrival
-        s_arrival = atomicAdd(p.counters + rb, 1);
-        __threadfence();
+        s_arrival = atomicAdd(p.counters + rb, 1);   // (the finisher reads the partials with loads served by L2, after this atomic)
       }
       __syncthreads();
-      HTR_TRACE(4);
       finish = (s_arrival == contributors - 1);
       if (finish) {
         const float* slot0 = p.part + (size_t)rb * p.slots * (MT * 128);
@@ -504,10 +510,17 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
       }
     }
     if (cgi == CG) { cgi = 0; ++rb; }
-    HTR_TRACE(5);
+    if (u < u_end) {
+      // the next row block of the range: the ring has run empty (every copy group issued for the old block has been consumed);
+      // its weights are fetched while the block's reduction above is still in flight on other warps
+      open_row_block(rb, cgi, u_end - u);
+      stage_bytes = 0;
+      refill_bytes = (kStages - 1) * kStageBytes;
+#pragma unroll
+      for (int sgi = 0; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
+    }
   }
   async_wait<0>();
-  HTR_TRACE(6);
 }
 
 // HTR_GEMV_OVERLAP=0 in the environment launches without programmatic stream serialisation (for A/B timing)

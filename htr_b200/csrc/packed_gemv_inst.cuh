@@ -21,7 +21,7 @@ template <int K, int MT>
 static int launch_one(const GemvParams& p, int grid, cudaStream_t stream) {
   if (const int e = allow_smem<K, MT>()) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = p.split > 0 ? dim3(p.split, grid / p.split) : dim3(grid);   // split form: (parts of a row block, row blocks)
   cfg.blockDim = dim3(kGemvThreads);
   cfg.dynamicSmemBytes = gemv_smem_bytes<K, MT>();
   cfg.stream = stream;
@@ -66,10 +66,3 @@ int packed_gemv_ctas_per_sm<HTR_INST_K>(int mt_rows) {
 
 }  // namespace htr
 
-#ifdef HTR_GEMV_TRACE
-#if HTR_INST_K == 4
-extern "C" int htr_trace_read(unsigned long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, htr::htr_trace_buf, sizeof(unsigned long long) * n);
-}
-#endif
-#endif

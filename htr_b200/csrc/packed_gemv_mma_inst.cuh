@@ -1,57 +1,102 @@
 // Instantiates the warp-MMA packed GEMV for one stream width; included by packed_gemv_mma_k<K>.cu with HTR_INST_K set.
+#include <cstdlib>
+
 #include "packed_gemv_mma.cuh"
 
 namespace htr {
 
-template <int K, int NS>
+template <int K, int NB>
 static int allow_mma_smem() {
   static bool done[64] = {false};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev >= 0 && dev < 64 && done[dev]) return 0;
-  e = cudaFuncSetAttribute(packed_gemv_mma_kernel<K, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemv_mma_smem_bytes<K, NS>());
+  int optin = 0;
+  e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   if (e != cudaSuccess) return (int)e;
-  e = cudaFuncSetAttribute(packed_gemv_mma_kernel<K, NS>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  e = cudaFuncSetAttribute(packed_gemv_mma_kernel<K, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, optin - 4096);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaFuncSetAttribute(packed_gemv_mma_kernel<K, NB>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return (int)e;
   if (dev >= 0 && dev < 64) done[dev] = true;
   return 0;
 }
 
-template <int K, int NS>
+template <int K, int NB>
 static int launch_mma_one(const GemvParams& p, int grid, cudaStream_t stream) {
-  if (const int e = allow_mma_smem<K, NS>()) return e;
+  if (const int e = allow_mma_smem<K, NB>()) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = p.split > 0 ? dim3(p.split, grid / p.split) : dim3(grid);   // split form: (parts of a row block, row blocks)
   cfg.blockDim = dim3(kGemvThreads);
-  cfg.dynamicSmemBytes = gemv_mma_smem_bytes<K, NS>();
+  cfg.dynamicSmemBytes = mma_ring_bytes<K>() + mma_window_bytes(NB, p.wblocks);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = gemv_overlap_enabled() ? 1 : 0;
-  return (int)cudaLaunchKernelEx(&cfg, packed_gemv_mma_kernel<K, NS>, p);
+  return (int)cudaLaunchKernelEx(&cfg, packed_gemv_mma_kernel<K, NB>, p);
 }
 
-template <int K, int NS>
-static int occupancy_mma_one() {
-  int ctas = 0;
-  if (allow_mma_smem<K, NS>()) return -1;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, packed_gemv_mma_kernel<K, NS>, kGemvThreads, gemv_mma_smem_bytes<K, NS>()) != cudaSuccess)
-    return -1;
-  return ctas;
+// HTR_GEMV_MMA_CTAS in the environment: CTAs per SM the launches are planned for (2 leaves room for larger activation windows)
+static int mma_target_ctas() {
+  static const int value = [] {
+    const char* v = std::getenv("HTR_GEMV_MMA_CTAS");
+    const int t = v ? std::atoi(v) : 3;
+    return t < 1 || t > 4 ? 3 : t;
+  }();
+  return value;
 }
 
-// one MMA set serves two rows with four planes each, or four rows of 16-bit activations with two planes each
+template <int K, int NB>
+static int config_mma_one(int rows, int* ctas_per_sm, int* window_cap) {
+  if (const int e = allow_mma_smem<K, NB>()) return e;
+  int dev = 0, per_sm_bytes = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaDeviceGetAttribute(&per_sm_bytes, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev);
+  if (e != cudaSuccess) return (int)e;
+  cudaFuncAttributes fa;
+  e = cudaFuncGetAttributes(&fa, packed_gemv_mma_kernel<K, NB>);
+  if (e != cudaSuccess) return (int)e;
+  const int row_cap = kMmaItems / (rows < 1 ? 1 : rows);
+  for (int target = mma_target_ctas(); target >= 1; --target) {
+    // every resident CTA costs its static and dynamic shared memory plus 1 KB that the system reserves
+    const int budget = per_sm_bytes / target - 1024 - (int)fa.sharedSizeBytes - mma_ring_bytes<K>();
+    int cap = budget / (NB * 512);
+    if (cap > row_cap) cap = row_cap;
+    if (cap < 2 && target > 1) continue;
+    if (cap < 1) return (int)cudaErrorLaunchOutOfResources;
+    int ctas = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, packed_gemv_mma_kernel<K, NB>, kGemvThreads,
+                                                      mma_ring_bytes<K>() + mma_window_bytes(NB, cap));
+    if (e != cudaSuccess) return (int)e;
+    if (ctas < 1) continue;
+    *ctas_per_sm = ctas < target ? ctas : target;
+    *window_cap = cap;
+    return 0;
+  }
+  return (int)cudaErrorLaunchOutOfResources;
+}
+
 template <>
 int launch_packed_gemv_mma<HTR_INST_K>(const GemvParams& p, int grid, cudaStream_t stream) {
-  return mma_one_set(p.rows, p.dtype) ? launch_mma_one<HTR_INST_K, 1>(p, grid, stream) : launch_mma_one<HTR_INST_K, 2>(p, grid, stream);
+  return mma_b_columns(p.rows) == 4 ? launch_mma_one<HTR_INST_K, 4>(p, grid, stream) : launch_mma_one<HTR_INST_K, 8>(p, grid, stream);
 }
 
 template <>
-int packed_gemv_mma_ctas_per_sm<HTR_INST_K>(int rows, int dtype) {
-  return mma_one_set(rows, dtype) ? occupancy_mma_one<HTR_INST_K, 1>() : occupancy_mma_one<HTR_INST_K, 2>();
+int packed_gemv_mma_config<HTR_INST_K>(int rows, int* ctas_per_sm, int* window_cap) {
+  return mma_b_columns(rows) == 4 ? config_mma_one<HTR_INST_K, 4>(rows, ctas_per_sm, window_cap)
+                                  : config_mma_one<HTR_INST_K, 8>(rows, ctas_per_sm, window_cap);
 }
 
 }  // namespace htr
+
+#ifdef HTR_ABL_TRACE
+#if HTR_INST_K == 4
+extern "C" int htr_trace_read(unsigned long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, htr::htr_trace_buf, sizeof(unsigned long long) * n);
+}
+#endif
+#endif

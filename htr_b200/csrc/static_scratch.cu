@@ -37,6 +37,11 @@ std::mutex g_setup_mutex;
 extern "C" int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
                                  const uint8_t* su, const uint8_t* sv, const void* bias, void* y, htr_stream_t stream) {
   if (M == 0) return HTR_OK;
+  // the size check comes first: a call that is going to be refused puts nothing on the stream
+  if (mt > 0 && nt > 0 && M > 0 && M <= HTR_GEMV_MAX_ROWS && mt % 8 == 0 && nt % 8 == 0) {
+    const size_t need = htr_linear_workspace_bytes(M, mt * 16, nt * 16, K);
+    if (need > (size_t)HTR_STATIC_WORKSPACE_BYTES) return HTR_ERR_TOO_LARGE;
+  }
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return HTR_ERR_CUDA;
   void* scratch = nullptr;
@@ -52,10 +57,6 @@ extern "C" int htr_linear_static(const void* x, int dtype, int M, const void* qw
       s.ready = true;
     }
     scratch = s.scratch;
-  }
-  if (mt > 0 && nt > 0 && M > 0 && M <= HTR_GEMV_MAX_ROWS && mt % 8 == 0 && nt % 8 == 0) {
-    const size_t need = htr_linear_workspace_bytes(M, mt * 16, nt * 16, K);
-    if (need > (size_t)HTR_STATIC_WORKSPACE_BYTES) return HTR_ERR_TOO_LARGE;
   }
   return htr_linear_ex(x, dtype, M, qweight, mt, nt, K, scales, su, sv, bias, y, scratch, (size_t)HTR_STATIC_WORKSPACE_BYTES, stream, 0u);
 }

@@ -52,16 +52,10 @@ __device__ __forceinline__ float codebook_value(uint32_t hash, float inv_hi, flo
   return __fmaf_rn(v, inv_hi, __fmul_rn(v, inv_lo));
 }
 
-// packed float32 pairs (one instruction, two candidates); HTR_VIT_SCALAR builds the same arithmetic from scalar instructions
-#ifdef HTR_VIT_SCALAR
-__device__ __forceinline__ float2 add2(float2 a, float2 b) { return make_float2(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return make_float2(__fmul_rn(a.x, b.x), __fmul_rn(a.y, b.y)); }
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return make_float2(__fmaf_rn(a.x, b.x, c.x), __fmaf_rn(a.y, b.y, c.y)); }
-#else
+// packed float32 pairs: one instruction, two candidates
 __device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-#endif
 
 struct Best {
   float v;

@@ -60,6 +60,8 @@ class PackedDecoder:
         self.k_cache = torch.zeros(c.layers, c.max_len, c.kv_heads, c.head_dim, dtype=dtype, device=device)
         self.v_cache = torch.zeros_like(self.k_cache)
         self.arange = torch.arange(c.max_len, device=device)
+        # set by the glue kernels when a position lies outside the caches (htr_dec_rope_cache / _attention / _rope_attention)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
     @staticmethod
     def random_weights(cfg, device, seed=0, dtype=torch.bfloat16):
@@ -208,10 +210,11 @@ class PackedDecoder:
                                               T, c.hidden, c.eps, st), "htr_dec_add_rmsnorm")
             qkv = ops.linear(h, *L["qkv"])
             _lib.check(L_.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), q.data_ptr(),
-                                             self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st),
-                       "htr_dec_rope_cache")
+                                             self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim,
+                                             c.max_len, self.status.data_ptr(), st), "htr_dec_rope_cache")
             _lib.check(L_.htr_dec_attention(q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), pos.data_ptr(),
-                                            att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_attention")
+                                            att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, c.max_len, self.status.data_ptr(), st),
+                       "htr_dec_attention")
             o = ops.linear(att.view(T, c.q_heads * c.head_dim), *L["o"])
             _lib.check(L_.htr_dec_add_rmsnorm(x.data_ptr(), o.data_ptr(), L["ln2"].data_ptr(), h.data_ptr(), T, c.hidden, c.eps, st),
                        "htr_dec_add_rmsnorm")
@@ -237,13 +240,15 @@ class PackedDecoder:
             if T == 1:                                          # one token: rotary embedding, cache write and attention in one launch
                 _lib.check(L_.htr_dec_rope_attention(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(),
                                                      self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), att.data_ptr(),
-                                                     c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_rope_attention")
+                                                     c.q_heads, c.kv_heads, c.head_dim, c.max_len, self.status.data_ptr(), st),
+                           "htr_dec_rope_attention")
             else:
                 _lib.check(L_.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), self.cos.data_ptr(), self.sin.data_ptr(), q.data_ptr(),
-                                                 self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st),
-                           "htr_dec_rope_cache")
+                                                 self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim,
+                                                 c.max_len, self.status.data_ptr(), st), "htr_dec_rope_cache")
                 _lib.check(L_.htr_dec_attention(q.data_ptr(), self.k_cache[li].data_ptr(), self.v_cache[li].data_ptr(), pos.data_ptr(),
-                                                att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, st), "htr_dec_attention")
+                                                att.data_ptr(), T, c.q_heads, c.kv_heads, c.head_dim, c.max_len, self.status.data_ptr(), st),
+                       "htr_dec_attention")
             ops.linear_fused(att.view(T, c.q_heads * c.head_dim), *L["o"], out=x, residual=True)
             gu = ops.linear_fused(x, *L["gate_up"], prologue=ops.PROLOGUE_RMSNORM, norm_weight=L["ln2"], eps=c.eps)
             ops.linear_fused(gu, *L["down"], out=x, prologue=ops.PROLOGUE_SWIGLU, residual=True)
@@ -316,4 +321,6 @@ class PackedDecoder:
                 step()
         ev[2].record()
         torch.cuda.synchronize()
+        if int(self.status.item()):
+            raise _lib.HTRError(f"a decode step used a position outside the {self.cfg.max_len}-row caches (status {int(self.status.item())})")
         return out, ev[0].elapsed_time(ev[1]) * 1e-3, ev[1].elapsed_time(ev[2]) * 1e-3

@@ -19,6 +19,7 @@ All work is enqueued on the current torch stream without a host synchronisation,
 captured in a CUDA graph.  Nothing here runs on the CPU: without the CUDA library the import fails.
 """
 import os
+import threading
 
 import torch
 
@@ -35,7 +36,11 @@ GEMM_ROUTE_MAX = int(os.environ.get("HTR_GEMM_ROUTE_MAX", "512"))
 # on the GEMM is faster: 25 us against 41-44 us at 4096x12288, 190 us against 384-408 us on the 151936x4096 head)
 GEMV_ROUTE_MAX = min(GEMV_MAX_M, int(os.environ.get("HTR_GEMV_ROUTE_MAX", "4")))
 
-_FLAGS = 0          # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
+class _ThreadState(threading.local):
+    flags = 0       # flags of htr_linear_ex applied to every GEMV launch of this thread (see independent_inputs)
+
+
+_STATE = _ThreadState()
 
 _DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 _WORKSPACES = {}
@@ -93,7 +98,7 @@ def _gemv(x2, qweight, scales, su, sv, bias, out):
     st = torch.cuda.current_stream(x2.device).cuda_stream
     rc = _lib.lib.htr_linear_ex(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
                                 sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st,
-                                _FLAGS)
+                                _STATE.flags)
     _lib.check(rc, "htr_linear")
 
 
@@ -213,7 +218,7 @@ def linear_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset)
     arr = (ctypes.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
     rc = _lib.lib.htr_linear_peers(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
                                    sv.data_ptr(), None if bias is None else bias.data_ptr(), None, arr, len(peer_ptrs), int(elem_offset),
-                                   ws.data_ptr(), ws.numel(), st, _FLAGS)
+                                   ws.data_ptr(), ws.numel(), st, _STATE.flags)
     _lib.check(rc, "htr_linear_peers")
 
 
@@ -236,7 +241,7 @@ def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K
 def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, out=None):
     """One launch over `route.numel()` problems (htr_linear_routed): problem i multiplies activation row i // x_div of `x` by the
     packed matrix whose four tensor addresses sit in row route[i] of `tables` (four int64 CUDA tensors, one row per expert; a
-    zero weight address skips the problem) and writes row i of the result [count, m].  With prologue=PROLOGUE_SWIGLU the rows of
+    zero weight address, or a route entry outside the tables, skips the problem) and writes row i of the result [count, m].  With prologue=PROLOGUE_SWIGLU the rows of
     x are [gate | up] of 2n bf16 values.  Nothing touches the host: the routing result stays on the device."""
     count = route.numel()
     dev = x.device
@@ -249,7 +254,8 @@ def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, 
         raise _lib.HTRError("htr_linear_routed: unsupported sizes")
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
-        rc = _lib.lib.htr_linear_routed(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count, tables[0].data_ptr(),
+        rc = _lib.lib.htr_linear_routed(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count, int(tables[0].numel()),
+                                        tables[0].data_ptr(),
                                         tables[1].data_ptr(), tables[2].data_ptr(), tables[3].data_ptr(), mt, nt, K, out.data_ptr(), int(prologue),
                                         ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream)
         _lib.check(rc, "htr_linear_routed")
@@ -262,14 +268,12 @@ class independent_inputs:
     shards of one activation).  Such launches overlap their predecessor completely (HTR_LINEAR_INPUT_INDEPENDENT)."""
 
     def __enter__(self):
-        global _FLAGS
-        self._old = _FLAGS
-        _FLAGS = _FLAGS | _lib.INPUT_INDEPENDENT
+        self._old = _STATE.flags
+        _STATE.flags = self._old | _lib.INPUT_INDEPENDENT
         return self
 
     def __exit__(self, *exc):
-        global _FLAGS
-        _FLAGS = self._old
+        _STATE.flags = self._old
         return False
 
 

@@ -121,13 +121,14 @@ int htr_linear_static(const void* x, int dtype, int M, const void* qweight, int 
 #define HTR_PROLOGUE_RMSNORM 1
 #define HTR_PROLOGUE_SWIGLU 2
 
-/* Routed form of the grouped launch: problem i uses row route[i] of four DEVICE tables of device pointers (one row per expert;
- * a NULL qweight entry skips the problem), reads activation row i / x_div of the matrix at x (rows x_row_stride elements apart)
+/* Routed form of the grouped launch: problem i uses row route[i] of four DEVICE tables of device pointers (table_rows rows, one
+ * per expert; a NULL qweight entry, or a route entry outside [0, table_rows), skips the problem and leaves its output row
+ * untouched), reads activation row i / x_div of the matrix at x (rows x_row_stride elements apart)
  * and writes row i of y[count][m].  With x_div = top-k and route = the router's expert ids this is the gate_up launch of a
  * mixture-of-experts step with no pointer arithmetic on the host or in framework kernels; the down launch uses x_div = 1 and
  * prologue = HTR_PROLOGUE_SWIGLU, in which x holds [gate | up] rows of 2n bf16 values and the linear sees
  * silu(gate) * up.  Workspace as for htr_linear_grouped. */
-int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count,
+int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count, int table_rows,
                       const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
                       const uint8_t* const* sv_table, int mt, int nt, int K, void* y, int prologue, void* workspace,
                       size_t workspace_bytes, htr_stream_t stream);
@@ -177,20 +178,23 @@ int htr_dequant_w(const void* qweight, int mt, int nt, int K, const void* scales
  * HTRLinearMethod.apply, htr/vllm_plugin.py:130-138); the reference ships none of its own.
  *   add_rmsnorm : resid[rows,h] += delta (delta may be NULL); out = rmsnorm(resid, eps) * weight
  *   rope_cache  : rotary embedding (interleaved pairs) of the q and k parts of qkv[rows, (q_heads+2*kv_heads)*head_dim];
- *                 q -> q_out[rows,q_heads,head_dim]; k, v -> cache rows pos[row] of k_cache/v_cache[max_len,kv_heads,head_dim]
+ *                 q -> q_out[rows,q_heads,head_dim]; k, v -> cache rows pos[row] of k_cache/v_cache[capacity,kv_heads,head_dim]
  *   attention   : out[row,head,:] = softmax(q . K[0..pos[row]] / sqrt(head_dim)) V, grouped-query, head_dim == 128,
- *                 pos[row] < HTR_DEC_MAX_LEN
- *   swiglu      : out[rows,I] = silu(gate_up[:, :I]) * gate_up[:, I:] */
+ *                 pos[row] < min(capacity, HTR_DEC_MAX_LEN)
+ *   swiglu      : out[rows,I] = silu(gate_up[:, :I]) * gate_up[:, I:]
+ * `capacity` is the number of rows of the two caches.  The positions live in device memory, so the kernels check them: a row
+ * whose position is negative or not below the limit touches no cache row, gets zeros as its attention output, and ORs a bit into
+ * *status (device int, may be NULL; 1 = rope_cache, 2 = attention, 4 = rope_attention).  Nothing traps. */
 #define HTR_DEC_MAX_LEN 1024
 int htr_dec_add_rmsnorm(void* resid, const void* delta, const void* weight, void* out, int rows, int h, float eps, htr_stream_t stream);
 int htr_dec_rope_cache(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* q_out, void* k_cache,
-                       void* v_cache, int rows, int q_heads, int kv_heads, int head_dim, htr_stream_t stream);
+                       void* v_cache, int rows, int q_heads, int kv_heads, int head_dim, int capacity, int* status, htr_stream_t stream);
 int htr_dec_attention(const void* q, const void* k_cache, const void* v_cache, const int64_t* pos, void* out, int rows, int q_heads,
-                      int kv_heads, int head_dim, htr_stream_t stream);
+                      int kv_heads, int head_dim, int capacity, int* status, htr_stream_t stream);
 int htr_dec_swiglu(const void* gate_up, void* out, int rows, int intermediate, htr_stream_t stream);
 /* rope_cache + attention of a single-token step (one row) in one launch: the same values, the new key/value rows written once */
 int htr_dec_rope_attention(const void* qkv, const int64_t* pos, const float* cosv, const float* sinv, void* k_cache, void* v_cache,
-                           void* out, int q_heads, int kv_heads, int head_dim, htr_stream_t stream);
+                           void* out, int q_heads, int kv_heads, int head_dim, int capacity, int* status, htr_stream_t stream);
 
 /* Encoder-side search: tail-biting Viterbi over the bit-shift trellis, one tile per row of x[B][T] with weights w[B][T]
  * (float32, T <= 256; the encoder uses T = 256).  Replaces htr/reference.py:7-50 (viterbi) and the CUDA module of
@@ -206,22 +210,13 @@ int htr_viterbi(const float* x, const float* w, int B, int T, int K, int tailbit
 int htr_viterbi_last_cuda_error(void);
 int htr_codebook_f32(float* out, htr_stream_t stream);
 
-/* Launch-shape knobs of htr_linear for measurements (0 = library default): CTAs per SM of the GEMV grid. */
-void htr_set_gemv_ctas_per_sm(int ctas);
-/* Which kernel serves htr_linear and its variants for up to four activation rows: 0 = the CUDA-core GEMV, 1 = the tcgen05 GEMV
- * (hash words in tensor memory), 2 = the warp-MMA GEMV (hash words as mma.sync fragments), -1 = the default: environment
- * variable HTR_GEMV_TC if set, else by measurement (one row, and three or four float32 or fp16 rows: CUDA-core GEMV; two rows, and
- * three or four bf16 rows: warp-MMA GEMV).  Workspace sizes must be queried under the same setting as the call that
- * uses them. */
-void htr_set_gemv_tc(int mode);
+/* Which kernel serves htr_linear and its variants for up to four activation rows: 0 = the CUDA-core GEMV, 1 = the warp-MMA GEMV
+ * (hash words as int8 mma.sync fragments; one or two rows of any type, three or four bf16 rows), -1 = the default: environment
+ * variable HTR_GEMV_KERNEL if set, else the warp-MMA GEMV wherever it applies.  Grouped launches and five to eight rows always
+ * run on the CUDA-core GEMV.  (Measurement and test knob; no counterpart in the reference.) */
+void htr_set_gemv_kernel(int kind);
 /* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block);
-/* Number of thread blocks of the tensor-core GEMV (htr_linear with up to four rows) that gave up on a bounded wait since the
- * library was loaded on the current device; such a block writes NaN results.  Zero on a healthy system. */
-int htr_gemv_tc_failures(int* count);
-/* Where the last such block gave up: wait kind (1 = operand stage not released, 2 = operand stage not filled, 3 = window not
- * finished) << 28 | window of activations << 24 | unit of the block's range << 12 | block index.  0 when there was none. */
-int htr_gemv_tc_last_failure(unsigned* where);
 
 #ifdef __cplusplus
 }

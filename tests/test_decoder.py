@@ -114,7 +114,8 @@ def test_single_token_rope_attention_equals_the_two_kernels():
     inv = 1.0 / (1.0e6 ** (torch.arange(0, D, 2).float() / D))
     ang = torch.arange(max_len).float()[:, None] * inv[None, :]
     cos, sin = ang.cos().to(dev), ang.sin().to(dev)
-    for p in (0, 1, 7, 130, 299):
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for p in (0, 1, 7, 130, 299):                                           # 299 = the last row of the caches
         kc = torch.randn(max_len, hkv, D, generator=g).bfloat16().to(dev)
         vc = torch.randn(max_len, hkv, D, generator=g).bfloat16().to(dev)
         qkv = torch.randn(1, (hq + 2 * hkv) * D, generator=g).bfloat16().to(dev)
@@ -123,9 +124,11 @@ def test_single_token_rope_attention_equals_the_two_kernels():
         q = torch.empty(1, hq, D, dtype=torch.bfloat16, device=dev)
         want, got = torch.empty_like(q), torch.empty_like(q)
         _lib.check(L.htr_dec_rope_cache(qkv.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), q.data_ptr(), k1.data_ptr(), v1.data_ptr(),
-                                        1, hq, hkv, D, st), "htr_dec_rope_cache")
-        _lib.check(L.htr_dec_attention(q.data_ptr(), k1.data_ptr(), v1.data_ptr(), pos.data_ptr(), want.data_ptr(), 1, hq, hkv, D, st), "htr_dec_attention")
+                                        1, hq, hkv, D, max_len, status.data_ptr(), st), "htr_dec_rope_cache")
+        _lib.check(L.htr_dec_attention(q.data_ptr(), k1.data_ptr(), v1.data_ptr(), pos.data_ptr(), want.data_ptr(), 1, hq, hkv, D, max_len,
+                                       status.data_ptr(), st), "htr_dec_attention")
         _lib.check(L.htr_dec_rope_attention(qkv.data_ptr(), pos.data_ptr(), cos.data_ptr(), sin.data_ptr(), k2.data_ptr(), v2.data_ptr(), got.data_ptr(),
-                                            hq, hkv, D, st), "htr_dec_rope_attention")
+                                            hq, hkv, D, max_len, status.data_ptr(), st), "htr_dec_rope_attention")
         assert torch.equal(k1, k2) and torch.equal(v1, v2)                 # the same cache rows
         assert float((got.float() - want.float()).abs().max()) <= 2e-2 * float(want.float().abs().max())
+    assert int(status.item()) == 0                                          # every position was inside the caches

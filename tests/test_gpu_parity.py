@@ -257,3 +257,13 @@ def test_routed_launch_equals_one_call_per_problem(dev, K):
         if e != 3:
             want = ops.linear_fused(gu[i:i + 1].contiguous(), *experts[e], prologue=ops.PROLOGUE_SWIGLU)
             assert torch.equal(got[i:i + 1], want)
+    # route entries outside the tables are skipped like absent experts (the kernel compares them with the table length first)
+    wild = torch.tensor([0, E, 2, -1, 3, 1], dtype=torch.int64, device=dev)
+    x = torch.randn(T, n, device=dev)
+    out = torch.full((T * k, m), 7.0, device=dev)
+    ops.linear_routed(x, wild, tables, m // 16, n // 16, K, x_div=k, out=out)
+    for i, e in enumerate(wild.tolist()):
+        if e in (E, -1, 3):
+            assert bool((out[i] == 7.0).all())
+        else:
+            assert torch.equal(out[i:i + 1], ops.linear(x[i // k:i // k + 1], *experts[e]))

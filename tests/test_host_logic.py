@@ -72,8 +72,14 @@ def test_status_codes_without_touching_the_gpu(lib):
     assert L.htr_viterbi(None, None, 4, 256, 4, 1, None, None, None, 0, None) == -5
     assert L.htr_viterbi(None, None, 0, 256, 4, 1, None, None, None, 0, None) == 0
     assert L.htr_codebook_f32(None, None) == -5
-    assert L.htr_dec_rope_attention(None, None, None, None, None, None, None, 8, 2, 128, None) == -5
+    assert L.htr_dec_rope_attention(None, None, None, None, None, None, None, 8, 2, 128, 64, None, None) == -5
+    one = ctypes.c_int(0)
+    ptr = ctypes.addressof(one)                                             # any non-NULL address: the checks below come before a launch
+    assert L.htr_dec_rope_attention(ptr, ptr, ptr, ptr, ptr, ptr, ptr, 8, 2, 128, 0, None, None) == -2          # a cache without rows
+    assert L.htr_dec_attention(ptr, ptr, ptr, ptr, ptr, 1, 8, 2, 128, 0, None, None) == -2
+    assert L.htr_dec_rope_cache(ptr, ptr, ptr, ptr, ptr, ptr, ptr, 1, 8, 2, 128, -3, None, None) == -2
     assert L.htr_linear_grouped(None, 0, None, 8, 8, 4, None, None, None, None, 0, None, 0, None) == 0                    # no problems
+    assert L.htr_linear_routed(None, 0, 1, 128, None, 0, 0, None, None, None, None, 8, 8, 4, None, 0, None, 0, None) == -2  # tables without rows
 
 
 def test_kernel_decode_arithmetic_on_the_host(tmp_path):
