@@ -41,6 +41,10 @@ SHAPES = ((12288, 4096), (4096, 12288))      # (m out, n in): up/gate-like and d
 WIDTHS = (2, 3, 4, 5)
 COPIES = 8
 FALLBACK_HBM_GBS = 6650.0
+# DRAM traffic of one launch relative to its packed bytes, from the ncu capture of a launch of this workload
+TRAFFIC_RATIO = 1.0024
+TRAFFIC_NOTE = ("ncu dram__bytes_read+write on one 4096x12288 K4 launch of this workload: 25.25 MB for 25.19 MB algorithmic "
+                "(profiles/packed_gemv_K4_mlp_4096x12288_M1.md); 1.002x, proportional to packed bytes for the other widths")
 _CPU_CASES = []          # synthetic linears of the CPU sample, generated once per process
 
 
@@ -59,8 +63,8 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle sampling during the timed region (read-only)."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi clock / throttle sampling (read-only); `stop(window)` keeps the samples taken inside a wall-clock window."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
@@ -75,13 +79,10 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def lines(self):
-        try:
-            return sum(1 for _ in open(self.path))
-        except Exception:
-            return 0
+    def stop(self, window=None):
+        """window = (t0, t1) in time.time() seconds: only samples stamped inside it count (the timed region)."""
+        import datetime
 
-    def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -97,6 +98,10 @@ class ClockSampler:
                 if len(c) < 9:
                     continue
                 try:
+                    if window is not None:
+                        ts = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                        if ts < window[0] or ts > window[1]:
+                            continue
                     sm.append(float(c[1]))
                     mx.append(float(c[2]))
                 except ValueError:
@@ -177,6 +182,166 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def _time_graph(torch, dist, world, dev, fn, reps):
+    """ms per call of fn(): captured into a CUDA graph when possible, CUDA events, barrier on both sides, max over ranks."""
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    fn(); sync_all()
+    g = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(g):
+            fn()
+        run = g.replay
+    except Exception:
+        torch.cuda.synchronize()
+        run = fn
+    for _ in range(3):
+        run()
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    sync_all()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def _solo_group(dist, rank, world):
+    """A process group that holds this rank alone (every rank creates all of them, as torch.distributed requires)."""
+    mine = None
+    for r in range(world):
+        g = dist.new_group([r])
+        if r == rank:
+            mine = g
+    return mine
+
+
+def lm_head_record(torch, dist, rank, world, dev, reps):
+    """Benchmark configuration 3: LM head 151936x4096 K4, rows sharded over the ranks (strong scaling), the epilogue storing
+    into every rank's gather buffer; batch 1 and 8.  With several ranks the same head is also timed on one GPU in the same run
+    (every rank for itself), which gives the speed-up.  Three distinct heads rotate so that no launch finds its shard in L2."""
+    from htr_b200 import wire
+    from htr_b200.sharded import RowShardedLinear
+
+    m, n, K, copies = 151936, 4096, 4, 3
+    packed = [wire.random_packed(m, n, K, seed=300 + c, device=dev) for c in range(copies)]
+    solo = _solo_group(dist, rank, world) if world > 1 else None
+    sharded = [RowShardedLinear(*w, device=dev, gather="peer" if world > 1 else "nccl") for w in packed]
+    single = [RowShardedLinear(*w, device=dev, group=solo) for w in packed] if world > 1 else sharded
+    out = {"workload": "lm_head_151936x4096_K4_row_sharded",
+           "gather": "batch 1: epilogue peer stores + one cross-rank barrier; batch 8: local tensor-core GEMM + NCCL all-gather" if world > 1 else "none"}
+    for M in (1, 8):
+        x = torch.randn(M, n, device=dev, generator=torch.Generator(device=dev).manual_seed(M)).bfloat16()
+        if world > 1:
+            # one row runs on the integer-exact kernel in both forms: the gathered result must be the single-GPU result bit for bit.
+            # Eight rows: the shards run the 8-row GEMV, one GPU the tensor-core GEMM (float32 sums in different orders): bf16 rounding
+            for a, b in zip(sharded, single):
+                ya, yb = a(x), b(x)
+                if M == 1 and not torch.equal(ya, yb):
+                    raise RuntimeError("row-sharded LM head differs from the single-GPU result")
+                if M > 1 and not float((ya.float() - yb.float()).norm() / yb.float().norm()) <= 4e-3:
+                    raise RuntimeError("row-sharded LM head (batch 8) is not within bf16 rounding of the single-GPU result")
+        t_n = _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps) / copies
+        t_1 = _time_graph(torch, dist, world, dev, lambda: [h(x) for h in single], reps) / copies if world > 1 else t_n
+        out[f"batch{M}"] = {"us": round(1e3 * t_n, 2), "one_gpu_us": round(1e3 * t_1, 2), "speedup": round(t_1 / t_n, 3),
+                            "efficiency": round(t_1 / t_n / world, 3), "packed_GBps": round(payload_bytes(m, n, K) / (t_n * 1e-3) / 1e9, 1)}
+        if world > 1:
+            # where the time goes: the shard's kernel alone (no hand-over), and the other way of ordering the ranks
+            out[f"batch{M}"]["shard_kernel_only_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h.local(x) for h in sharded], reps) / copies, 2)
+            if M == 1:
+                from htr_b200 import sharded as sharded_mod
+                sharded_mod.PEER_ORDER = "flags"
+                out[f"batch{M}"]["with_delivery_flags_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps) / copies, 2)
+                sharded_mod.PEER_ORDER = "barrier"
+    if world > 1:
+        out["gather_check"] = "batch 1: bit-identical to the single-GPU result; batch 8: within bf16 rounding (4e-3 norm-relative)"
+    return out
+
+
+def moe_record(torch, dist, rank, world, dev, reps, tokens=(1, 8, 32)):
+    """Benchmark configuration 4: 64 experts, top-8, SwiGLU 4096 -> 1536 -> 4096, K3, experts dealt to the ranks; two routed
+    launches per rank and step, routing on the device, one CUDA graph.  With several ranks the whole layer is also timed on one
+    GPU in the same run."""
+    from htr_b200 import wire
+    from htr_b200.sharded import ExpertParallelMoE
+
+    E, h, inter, K = 64, 4096, 1536, 3
+    experts = [dict(gate_up=wire.random_packed(2 * inter, h, K, seed=2 * e, device=dev), down=wire.random_packed(h, inter, K, seed=2 * e + 1, device=dev))
+               for e in range(E)]
+    solo = _solo_group(dist, rank, world) if world > 1 else None
+    moe = ExpertParallelMoE(experts, device=dev)
+    moe1 = ExpertParallelMoE(experts, device=dev, group=solo) if world > 1 else moe
+    del experts
+    out = {"workload": "moe_64x_top8_swiglu_4096_1536_K3",
+           "combine": "peer stores of the gate-weighted parts + one cross-rank barrier + rank-ordered add" if world > 1 else "none"}
+    g = torch.Generator().manual_seed(0)
+    for T in tokens:
+        x = torch.randn(T, h, generator=g).bfloat16().to(dev)
+        ids = torch.stack([torch.randperm(E, generator=g)[:8] for _ in range(T)]).to(dev)
+        w = torch.rand(T, 8, generator=g)
+        w = (w / w.sum(-1, keepdim=True)).to(dev)
+        if world > 1:
+            a, b = moe(x, ids, w).float(), moe1(x, ids, w).float()
+            err = float((a - b).norm() / b.norm())
+            if not err <= 1e-2:
+                raise RuntimeError(f"expert-parallel MoE differs from the single-GPU layer: {err}")
+        t_n = _time_graph(torch, dist, world, dev, lambda: moe(x, ids, w), reps)
+        t_1 = _time_graph(torch, dist, world, dev, lambda: moe1(x, ids, w), reps) if world > 1 else t_n
+        out[f"tokens{T}"] = {"ms": round(t_n, 4), "one_gpu_ms": round(t_1, 4), "speedup": round(t_1 / t_n, 3)}
+    return out
+
+
+def batch_sweep_record(torch, dev, weights_by_k, reps):
+    """Benchmark configuration 1 beyond batch 1: the 4096x12288 linears at batch 1, 4, 8, 16, 64 for every width, over the
+    resident copies of the main workload (more than L2 per width), stream-ordered launches through ops.linear, one CUDA graph."""
+    from htr_b200 import ops
+
+    out = {"shape_m_x_n": [4096, 12288], "launch_form": "stream-ordered", "kernels": {"1": "packed_gemv_kernel<K,1>", "4": "packed_gemv_mma_kernel<K,8>",
+                                                                                      "8": "packed_gemm_tc_kernel<K>", "16": "packed_gemm_tc_kernel<K>", "64": "packed_gemm_tc_kernel<K>"}}
+    for K, ws in weights_by_k.items():
+        n = ws[0][0].shape[1] * 16
+        nbytes = payload_bytes(ws[0][0].shape[0] * 16, n, K)
+        row = {}
+        for M in (1, 4, 8, 16, 64):
+            x = torch.randn(M, n, device=dev, generator=torch.Generator(device=dev).manual_seed(M)).bfloat16()
+            ms = _time_graph(torch, None, 1, dev, lambda: [ops.linear(x, *w) for w in ws], reps) / len(ws)
+            row[f"M{M}"] = {"us": round(1e3 * ms, 2), "packed_GBps": round(nbytes / (ms * 1e-3) / 1e9, 1)}
+        out[f"K{K}"] = row
+    return out
+
+
+def decoder_record(torch, dist, rank, world, dev):
+    """Benchmark configuration 2: the dense 9B-class decoder (36 layers, K4 trunk and head), 16-token prompt, 256 greedy tokens,
+    batch 1, one CUDA graph per decode step.  Several ranks = that many replicas (the trunk does not shard)."""
+    from htr_b200.decoder import DecoderConfig, PackedDecoder
+
+    model = PackedDecoder(DecoderConfig(), dev, seed=1 + rank)
+    prompt = torch.randint(0, 151936, (16,), generator=torch.Generator().manual_seed(2 + rank))
+    model.generate(prompt, 8)                               # warm-up
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    toks, t_prompt, t_decode = model.generate(prompt, 256)
+    t = torch.tensor([t_prompt, t_decode], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    t_prompt, t_decode = float(t[0]), float(t[1])
+    bpt = model.packed_bytes_per_token()
+    del model
+    torch.cuda.empty_cache()
+    return {"workload": "dense_9b_class_K4_trunk_K4_head", "prompt": 16, "new_tokens": 256, "batch": 1, "tokens_per_s": round(world * 256 / t_decode, 2),
+            "prompt_s": round(t_prompt, 4), "decode_s": round(t_decode, 4), "packed_bytes_per_token": bpt,
+            "packed_GBps_per_gpu": round(bpt * 256 / t_decode / 1e9, 1), "parallelism": "replicas only" if world > 1 else "one GPU"}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -237,7 +402,7 @@ def run_ours(args):
     # device->host copy; the items hold views of the pools
     for items in groups:
         n_in = sum(it["n"] for it in items)
-        n_out = sum(max(world, 1) * it["m"] for it in items)
+        n_out = sum(it["m"] for it in items)                     # a rank returns its own rows
         xh_pool, xd_pool = torch.empty(n_in, dtype=torch.bfloat16).pin_memory(), torch.empty(n_in, dtype=torch.bfloat16, device=dev)
         yh_pool, yd_pool = torch.empty(n_out, dtype=torch.bfloat16).pin_memory(), torch.empty(n_out, dtype=torch.bfloat16, device=dev)
         at = 0
@@ -251,6 +416,8 @@ def run_ours(args):
     side = torch.cuda.Stream(device=dev)
     gather_mode = os.environ.get("HTR_BENCH_GATHER", "peer") if world > 1 else "none"
     hdl = None
+    flags = flag_ptrs = epoch = wait_status = None
+    peer_order = os.environ.get("HTR_BENCH_PEER_ORDER", "barrier")    # "flags": delivery flags raised by the kernels + one bounded wait per K-group
     if gather_mode == "peer":
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
@@ -265,6 +432,15 @@ def run_ours(args):
                 it["gathered"] = pool[off:off + world * it["m"]].view(world, it["m"])
                 it["peers"] = [b + off * 2 for b in bases]
                 off += world * it["m"]
+        # delivery flags instead of a barrier: word r of a rank's array counts the launches of rank r whose rows have arrived there
+        flags = symm_mem.empty(64, dtype=torch.int32, device=dev)
+        flags.zero_()
+        fh = symm_mem.rendezvous(flags, dist.group.WORLD)
+        flag_ptrs = [int(p) + 4 * rank for p in fh.buffer_ptrs]
+        epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        wait_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        dist.barrier()
 
     def run_group(items, from_host=False):
         main = torch.cuda.current_stream()
@@ -275,7 +451,7 @@ def run_ours(args):
         for it in items:
             xin = it["xd"] if from_host else it["x"]
             if gather_mode == "peer":
-                ops.linear_into_peers(xin, *it["w"], None, it["peers"], rank * it["m"])
+                ops.linear_into_peers(xin, *it["w"], None, it["peers"], rank * it["m"], flag_ptrs if peer_order == "flags" else None)
                 continue
             y = ops.linear(xin, *it["w"])
             if gather_mode == "nccl":
@@ -283,15 +459,21 @@ def run_ours(args):
                 with torch.cuda.stream(side):
                     dist.all_gather_into_tensor(it["gathered"], y)
                 y.record_stream(side)
-                outs.append(it["gathered"].view(-1))
+                outs.append(it["gathered"][rank])
             else:
                 outs.append(y.view(-1))
         if gather_mode == "nccl":
             main.wait_stream(side)
         if gather_mode == "peer":
-            hdl.barrier(channel=0)
-            outs = [it["gathered"].view(-1) for it in items]
+            # one bounded wait for the group: every rank has delivered the rows of all its launches (nobody reads the peers' rows in
+            # the timed passes, so a rank that runs ahead may already overwrite them for the next pass)
+            if peer_order == "flags":
+                ops.peer_wait(flags, epoch, world, wait_status, count=len(items))
+            else:
+                hdl.barrier(channel=0)
+            outs = [it["gathered"][rank] for it in items]
         if from_host:
+            # the consumer of a gathered result sits on one host: every rank returns its own rows (together they are the result)
             torch.cat(outs, out=yd_pool)
             yh_pool.copy_(yd_pool, non_blocking=True)
 
@@ -300,6 +482,24 @@ def run_ours(args):
         run_group(items)
         run_group(items, from_host=True)
     torch.cuda.synchronize()
+
+    # N > 1: what the timed passes gather must be what every rank computed.  Each rank fingerprints its own rows (the operator's
+    # plain output), the fingerprints travel by NCCL, and every rank compares them with the rows it received from its peers.
+    gather_check = None
+    if world > 1:
+        def fingerprint(t):
+            v = t.contiguous().view(torch.int16).to(torch.int64)
+            return torch.stack([v.sum(), (v * torch.arange(1, v.numel() + 1, device=v.device)).sum()])
+        for items in groups:
+            it = items[0]
+            run_group(items)
+            mine = fingerprint(ops.linear(it["x"], *it["w"]).view(-1))
+            every = torch.empty(world, 2, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(every, mine)
+            for r in range(world):
+                if not torch.equal(fingerprint(it["gathered"][r]), every[r]):
+                    raise RuntimeError(f"rank {rank}: the rows gathered from rank {r} differ from what that rank computed")
+        gather_check = "bit-identical: every rank's gathered rows carry the fingerprint of the rank that computed them (one linear per K)"
     use_graphs = not args.no_graphs
 
     graph_note = []
@@ -328,8 +528,8 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(graphs, steps, from_host=False, independent=False):
-        """K steps bracketed by a barrier; returns (total ms, [ms per K-group per step])."""
+    def timed(graphs, steps, passes, from_host=False, independent=False):
+        """`steps` steps of `passes` passes each, bracketed by a barrier; returns (total ms, [ms per K-group per step], wall window)."""
         def one_pass(marks=None):
             for i, items in enumerate(groups):
                 if marks is not None:
@@ -346,35 +546,47 @@ def run_ours(args):
         for _ in range(max(3, args.warmup)):
             one_pass()
         barrier()
+        # per-width times come from the first pass of every step; the total covers all passes
         marks = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in groups] for _ in range(steps)]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
         e0.record()
         for s in range(steps):
             one_pass(marks[s])
+            for _ in range(passes - 1):
+                one_pass()
         e1.record()
         barrier()
-        return e0.elapsed_time(e1), [sum(marks[s][i][0].elapsed_time(marks[s][i][1]) for s in range(steps)) / steps for i in range(len(groups))]
+        w1 = time.time()
+        return e0.elapsed_time(e1), [sum(marks[s][i][0].elapsed_time(marks[s][i][1]) for s in range(steps)) / steps for i in range(len(groups))], (w0, w1)
 
+    # The linears of a pass do not feed one another, so they are launched the way the library asks for such work:
+    # declared independent of their predecessor (HTR_LINEAR_INPUT_INDEPENDENT), which lets consecutive launches overlap.
+    g_ind = capture(independent=True) if use_graphs else None
+    # a step is `passes` passes over the workload, chosen so that the timed region lasts about a second (clock samples then
+    # come from inside it); every rank uses rank 0's count
+    probe_ms, _, _ = timed(g_ind, 2, 1, independent=True)
+    passes = args.passes if args.passes > 0 else max(1, int(1050.0 / max(probe_ms / 2 * args.steps, 1e-3) + 0.999))
+    if world > 1:
+        pt = torch.tensor([passes], device=dev)
+        dist.broadcast(pt, 0)
+        passes = int(pt[0])
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    # The linears of a pass do not feed one another, so they are launched the way the library asks for such work:
-    # declared independent of their predecessor (HTR_LINEAR_INPUT_INDEPENDENT), which lets consecutive launches overlap.
-    ms, per_k_ms = timed(capture(independent=True) if use_graphs else None, args.steps, independent=True)
+    ms, per_k_ms, window = timed(g_ind, args.steps, passes, independent=True)
+    clocks = sampler.stop(window) if rank == 0 else None
     # the same pass in the default, stream-ordered form (what a chain of dependent linears gets)
-    ov_ms, ov_per_k_ms = timed(capture() if use_graphs else None, args.steps)
+    side_passes = max(1, passes // 4)
+    ov_ms, ov_per_k_ms, _ = timed(capture() if use_graphs else None, args.steps, side_passes)
     # end to end through the public operator: activations from pinned host memory, outputs back to pinned host memory
     e2e_steps = max(1, min(args.steps, 10))
-    e2e_ms, _ = timed(capture(independent=True, from_host=True) if use_graphs else None, e2e_steps, from_host=True, independent=True)
-    if rank == 0 and world == 1:
-        # the timed regions last a fraction of a second; keep the same load up (untimed) until the sampler has a few samples
-        t_end = time.time() + 2.0
-        while sampler.lines() < 5 and time.time() < t_end:
-            timed(None, 1, independent=True)
-    clocks = sampler.stop() if rank == 0 else None
+    e2e_ms, _, _ = timed(capture(independent=True, from_host=True) if use_graphs else None, e2e_steps, side_passes, from_host=True, independent=True)
     h2d = sum(items[0]["pools"][0].numel() * 2 for items in groups)
     d2h = sum(items[0]["pools"][2].numel() * 2 for items in groups)
 
+    if wait_status is not None and int(wait_status.item()):
+        raise RuntimeError(f"rank {rank}: a bounded wait for peer deliveries ran out (status {int(wait_status.item())})")
     if world > 1:
         t = torch.tensor([ms, e2e_ms, ov_ms] + per_k_ms + ov_per_k_ms, device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -382,36 +594,57 @@ def run_ours(args):
         per_k_ms = [float(v) for v in t[3:3 + len(groups)]]
         ov_per_k_ms = [float(v) for v in t[3 + len(groups):]]
 
+    # ---- the other benchmark configurations, as extra keys of the same line (after the headline passes)
+    extras = {}
+    if not args.no_extras:
+        if world == 1:
+            by_k = {K: [it["w"] for it in items if it["m"] == 4096] for K, items in zip(WIDTHS, groups)}
+            extras["batch_sweep"] = batch_sweep_record(torch, dev, by_k, max(3, args.steps // 2))
+            del by_k
+        # free the headline workload before the larger models are built
+        groups.clear()
+        del g_ind
+        torch.cuda.empty_cache()
+        if world == 1:
+            extras["decoder"] = decoder_record(torch, dist, rank, world, dev)
+        extras["lm_head_strong"] = lm_head_record(torch, dist, rank, world, dev, max(5, args.steps))
+        torch.cuda.empty_cache()
+        extras["moe_ep"] = moe_record(torch, dist, rank, world, dev, max(5, args.steps))
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         job_bytes = total_bytes * world
-        value = job_bytes * args.steps / (ms * 1e-3) / 1e9
-        e2e_value = job_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+        value = job_bytes * args.steps * passes / (ms * 1e-3) / 1e9
+        e2e_value = job_bytes * e2e_steps * side_passes / (e2e_ms * 1e-3) / 1e9
         per_k = {}
         for i, K in enumerate(WIDTHS):
             kb = sum(payload_bytes(m, n, K) for (m, n) in SHAPES) * COPIES
             gbs = kb / (per_k_ms[i] * 1e-3) / 1e9
             per_k[f"K{K}"] = {"GBps_per_gpu": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                               "us_per_launch": round(1e3 * per_k_ms[i] / (len(SHAPES) * COPIES), 3)}
-        ogbs = total_bytes * args.steps / (ov_ms * 1e-3) / 1e9
+        ogbs = total_bytes * args.steps * side_passes / (ov_ms * 1e-3) / 1e9
         overlapped = {"what": "same pass, default launch form: every launch waits for its predecessor before reading activations",
-                      "value": ogbs * world, "unit": "GB/s", "frac_of_peak_per_gpu": ogbs / peak,
+                      "value": ogbs * world, "unit": "GB/s", "frac_of_peak_per_gpu": ogbs / peak, "passes_per_step": side_passes,
                       "per_K": {f"K{K}": round(sum(payload_bytes(m, n, K) for (m, n) in SHAPES) * COPIES / (ov_per_k_ms[i] * 1e-3) / 1e9, 1)
                                 for i, K in enumerate(WIDTHS)}}
-        achieved = total_bytes * args.steps / (ms * 1e-3) / 1e9     # per GPU: one kernel family, launches back to back
+        achieved = total_bytes * args.steps * passes / (ms * 1e-3) / 1e9     # per GPU: one kernel family, launches back to back
         line = base_line(args)
-        line.update(value=value, ms_per_step=ms / args.steps, gpu_launches=launches * args.steps, clocks=clocks,
-                    e2e={"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        line["config"]["passes_per_step"] = passes
+        line.update(value=value, ms_per_step=ms / args.steps, timed_region_s=ms * 1e-3, gpu_launches=launches * args.steps * passes, clocks=clocks,
+                    e2e={"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d * side_passes, "d2h_bytes_per_step": d2h * side_passes,
+                         "steps": e2e_steps, "passes_per_step": side_passes,
+                         "returns": "every rank copies its own rows back to its host" if world > 1 else "all outputs"},
                     roofline={"bound": "hbm", "kernel": "packed_gemv_kernel<K,1>", "achieved": achieved, "peak": peak, "unit": "GB/s",
                               "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
-                              "traffic_note": "ncu dram__bytes_read+write on one 4096x12288 K4 launch of this workload: 25.25 MB for "
-                                              "25.19 MB algorithmic (profiles/packed_gemv_K4_mlp_4096x12288_M1.md); 1.002x, "
-                                              "proportional to packed bytes for the other widths",
-                              "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / launches,
+                              "traffic_note": TRAFFIC_NOTE,
+                              "bytes_per_launch_avg": total_bytes / launches, "us_per_launch_avg": 1e3 * ms / args.steps / passes / launches,
                               "per_K": per_k},
                     stream_ordered=overlapped,
                     timing="cuda events on the launch stream; " + ("one CUDA graph per K-group" if use_graphs and not graph_note else "eager launches " + "; ".join(graph_note)))
-        line["roofline"]["traffic"] = round(1.0024 * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
+        line["roofline"]["traffic"] = round(TRAFFIC_RATIO * total_bytes / launches)     # scaled from the captured launch (see traffic_note)
+        if gather_check:
+            line["gather_check"] = gather_check
+        line.update(extras)
         if world == 1 and not args.no_cpu:
             gbs, dt, threads, sample = cpu_sample()
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample, "seconds": dt}
@@ -421,15 +654,14 @@ def run_ours(args):
 
 
 def run_extra(args):
-    """Further workloads of the benchmark configurations, one GPU (or N ranks for the sharded LM head):
+    """The other benchmark configurations on their own (the default run carries them as extra keys of its line):
     lmhead   151936x4096 K4 LM head, batch 1 and 8, rows sharded over the ranks (strong scaling), peer-store gather
-    decoder  the 9B-class dense decoder, K4 trunk + K4 head, 16-token prompt + 256 greedy tokens, one sequence
-    moe      64 experts, top-8, SwiGLU 4096->1536->4096, K3, 1..32 tokens per step
+    decoder  the 9B-class dense decoder, K4 trunk + K4 head, 16-token prompt + 256 greedy tokens, one sequence per rank
+    moe      64 experts, top-8, SwiGLU 4096->1536->4096, K3, 1..32 tokens per step, experts dealt to the ranks
     viterbi  the encoder's trellis search: 1024 tiles per call (the reference encoder's batch), K2..K5, with a CPU sample
     Prints one JSON line per workload (rank 0)."""
     import torch
     import torch.distributed as dist
-    from htr_b200 import ops, wire
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -438,94 +670,22 @@ def run_extra(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    peak, peak_kind = measured_peak()
-
-    def sync_all():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
 
     def time_graph(fn, reps):
-        fn(); sync_all()
-        g = torch.cuda.CUDAGraph()
-        try:
-            with torch.cuda.graph(g):
-                fn()
-            run = g.replay
-        except Exception:
-            torch.cuda.synchronize()
-            run = fn
-        for _ in range(3):
-            run()
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            run()
-        e1.record()
-        sync_all()
-        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
+        return _time_graph(torch, dist, world, dev, fn, reps)
 
     if args.workload == "lmhead":
-        from htr_b200.sharded import RowShardedLinear
-        m, n, K = 151936, 4096, 4
-        copies = 3                                              # distinct heads rotate so that no launch finds its shard in L2
-        heads = []
-        for c in range(copies):
-            qw, sc, su, sv = wire.random_packed(m, n, K, seed=300 + c)
-            heads.append(RowShardedLinear(qw, sc, su, sv, device=dev, gather="peer" if world > 1 else "nccl"))
-        for M in (1, 8):
-            x = torch.randn(M, n, device=dev).bfloat16()
-            ms = time_graph(lambda: [h(x) for h in heads], args.steps) / copies
-            if rank == 0:
-                gbs = payload_bytes(m, n, K) / (ms * 1e-3) / 1e9
-                print(json.dumps({"metric": "lm_head_packed_GBps", "unit": "GB/s", "value": gbs, "n_gpus": world, "scaling": "strong",
-                                  "ms_per_step": ms, "frac_of_peak_per_gpu": gbs / world / peak, "tokens_per_s": M / (ms * 1e-3),
-                                  "config": {"workload": "lm_head_151936x4096_K4_row_sharded", "batch": M, "gather": "peer stores + barrier" if world > 1 else "none"}}), flush=True)
-    elif args.workload == "decoder":
-        # the dense trunk does not shard (an all-gather per linear would cost more than the step): N GPUs = N replicas, each
-        # decoding its own sequence; the aggregate counts all of them over the slowest rank's time
-        from htr_b200.decoder import DecoderConfig, PackedDecoder
-        model = PackedDecoder(DecoderConfig(), dev, seed=1 + rank)
-        prompt = torch.randint(0, 151936, (16,), generator=torch.Generator().manual_seed(2 + rank))
-        model.generate(prompt, 8)                               # warm-up
-        sync_all()
-        toks, t_prompt, t_decode = model.generate(prompt, 256)
-        t = torch.tensor([t_prompt, t_decode], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        t_prompt, t_decode = float(t[0]), float(t[1])
-        bpt = model.packed_bytes_per_token()
+        rec = lm_head_record(torch, dist, rank, world, dev, args.steps)
         if rank == 0:
-            print(json.dumps({"metric": "decode_tokens_per_s", "unit": "tok/s", "value": world * 256 / t_decode, "n_gpus": world,
-                              "scaling": "weak", "wall_tokens_per_s_incl_prompt": world * 256 / (t_prompt + t_decode), "prompt_s": t_prompt,
-                              "decode_s": t_decode, "packed_GBps": world * bpt * 256 / t_decode / 1e9,
-                              "frac_of_peak_per_gpu": bpt * 256 / t_decode / 1e9 / peak, "packed_bytes_per_token": bpt,
-                              "config": {"workload": "dense_9b_class_K4_trunk_K4_head", "prompt": 16, "new_tokens": 256, "batch": 1,
-                                         "weights": "random packed", "graph": "one CUDA graph per decode step",
-                                         "parallelism": "replicas only" if world > 1 else "one GPU"}}), flush=True)
+            print(json.dumps({"metric": "lm_head_us", "unit": "us", "higher_is_better": False, "n_gpus": world, "scaling": "strong", **rec}), flush=True)
+    elif args.workload == "decoder":
+        rec = decoder_record(torch, dist, rank, world, dev)
+        if rank == 0:
+            print(json.dumps({"metric": "decode_tokens_per_s", "unit": "tok/s", "value": rec["tokens_per_s"], "n_gpus": world, "scaling": "weak", **rec}), flush=True)
     elif args.workload == "moe":
-        from htr_b200.sharded import ExpertParallelMoE
-        E, h, inter, K = 64, 4096, 1536, 3
-        experts = [dict(gate_up=wire.random_packed(2 * inter, h, K, seed=2 * e), down=wire.random_packed(h, inter, K, seed=2 * e + 1)) for e in range(E)]
-        moe = ExpertParallelMoE(experts, device=dev)
-        g = torch.Generator().manual_seed(0)
-        for T in (1, 4, 8, 32):
-            x = torch.randn(T, h, generator=g).bfloat16().to(dev)
-            ids = torch.stack([torch.randperm(E, generator=g)[:8] for _ in range(T)])
-            w = torch.rand(T, 8, generator=g); w = (w / w.sum(-1, keepdim=True)).to(dev)
-            ids_d = ids.to(dev)
-            ms = time_graph(lambda: moe(x, ids_d, w), args.steps)          # grouped launches, routing on the device, graph replay
-            active = len(set(ids.flatten().tolist()))
-            nbytes = active * (payload_bytes(2 * inter, h, K) + payload_bytes(h, inter, K)) / max(world, 1)
-            if rank == 0:
-                print(json.dumps({"metric": "moe_layer_ms", "unit": "ms", "value": ms, "higher_is_better": False, "n_gpus": world,
-                                  "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "packed_GBps_per_gpu": nbytes / (ms * 1e-3) / 1e9,
-                                  "config": {"workload": "moe_64x_top8_swiglu_4096_1536_K3", "tokens": T, "routing": "on device; two grouped GEMV launches per layer (gate_up, down), CUDA graph"}}), flush=True)
+        rec = moe_record(torch, dist, rank, world, dev, args.steps, tokens=(1, 4, 8, 32))
+        if rank == 0:
+            print(json.dumps({"metric": "moe_layer_ms", "unit": "ms", "higher_is_better": False, "n_gpus": world, **rec}), flush=True)
     elif args.workload == "viterbi":
         from htr_b200 import encoder
         B = 1024                                                 # max_batch of the reference encoder (htr/encode.py:47)
@@ -594,6 +754,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    ap.add_argument("--passes", type=int, default=0, help="passes over the workload per step (0 = as many as make the timed region last about a second)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the extra keys (batch sweep, decoder, LM head, MoE)")
     ap.add_argument("--workload", default="mlp", choices=("mlp", "lmhead", "decoder", "moe", "viterbi"),
                     help="mlp = the default benchmark line; the others print lines for the remaining configurations")
     ap.add_argument("--real-streams", action="store_true",

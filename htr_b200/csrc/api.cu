@@ -198,7 +198,7 @@ extern "C" {
 static int launch_linear(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
                          const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
                          int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags,
-                         int prologue = 0, const void* norm_w = nullptr, float eps = 0.f, int residual = 0);
+                         int prologue = 0, const void* norm_w = nullptr, float eps = 0.f, int residual = 0, unsigned* const* peer_flags = nullptr);
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
                           const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
@@ -257,7 +257,8 @@ size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
     if (make_plan(M, m, n, K, &mma, 1) != HTR_OK) return 0;
     if ((size_t)mma.slots > slots) slots = (size_t)mma.slots;
   }
-  return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * sizeof(float);
+  // up to two rows may be asked for in the integer-exact form, whose partial sums are 64-bit
+  return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * (M <= 2 ? sizeof(long long) : sizeof(float));
 }
 
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block) {
@@ -289,6 +290,14 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
                        workspace_bytes, stream, flags);
 }
 
+int htr_linear_peers_signal(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                            const uint8_t* sv, const void* bias, void* const* peer_y, unsigned* const* peer_flags, int npeer, int64_t peer_offset,
+                            void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags) {
+  if (!peer_flags) return HTR_ERR_NULL;
+  return launch_linear(x, dtype, M, nt * 16, qweight, mt, nt, K, scales, su, sv, bias, nullptr, mt * 16, peer_y, npeer, peer_offset, workspace,
+                       workspace_bytes, stream, flags, 0, nullptr, 0.f, 0, peer_flags);
+}
+
 int htr_linear_padded(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
                       const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* workspace, size_t workspace_bytes,
                       htr_stream_t stream) {
@@ -312,11 +321,16 @@ int htr_linear_fused(const void* x, int M, const void* qweight, int mt, int nt, 
 static int launch_linear(const void* x, int dtype, int M, int n_in, const void* qweight, int mt, int nt, int K, const void* scales,
                          const uint8_t* su, const uint8_t* sv, const void* bias, void* y, int m_out, void* const* peer_y, int npeer,
                          int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream, unsigned flags, int prologue,
-                         const void* norm_w, float eps, int residual) {
+                         const void* norm_w, float eps, int residual, unsigned* const* peer_flags) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (M < 0 || M > HTR_GEMV_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
-  if (mt / 8 > kCounterBytes / 4 || (long long)(mt / 8) * (nt / 4) > 0x3FFFFFFFll) return HTR_ERR_TOO_LARGE;
+  if (mt / 8 > kDoneCounter || (long long)(mt / 8) * (nt / 4) > 0x3FFFFFFFll) return HTR_ERR_TOO_LARGE;
+  if (peer_flags) {
+    if (npeer < 1) return HTR_ERR_BAD_SHAPE;
+    for (int i = 0; i < npeer; ++i)
+      if (!peer_flags[i]) return HTR_ERR_NULL;
+  }
   if (M == 0) return HTR_OK;
   if (npeer < 0 || npeer > 8 || (npeer > 0 && !peer_y) || peer_offset < 0 || (peer_offset & 7)) return HTR_ERR_BAD_SHAPE;
   if (!x || !qweight || !scales || !su || !sv || (!y && npeer == 0)) return HTR_ERR_NULL;
@@ -327,10 +341,12 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
     return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
   Plan pl;
-  const int kind = gemv_kind(M, dtype);
+  // the integer-exact form: up to two rows (four byte planes per activation), plain activations
+  const bool exact = (flags & HTR_LINEAR_EXACT_SUMS) && M <= 2 && prologue == 0;
+  const int kind = exact ? 1 : gemv_kind(M, dtype);
   const int rc = make_plan(M, m, n, K, &pl, kind);
   if (rc != HTR_OK) return rc;
-  const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * sizeof(float);
+  const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * (exact ? sizeof(long long) : sizeof(float));
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
 
   GemvParams p;
@@ -371,8 +387,10 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.npeer = npeer;
   p.peer_offset = peer_offset;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = i < npeer ? peer_y[i] : nullptr;
+  for (int i = 0; i < 8; ++i) p.peer_flag[i] = (peer_flags && i < npeer) ? peer_flags[i] : nullptr;
   p.slots = pl.slots;
   p.wblocks = pl.wblocks;
+  p.exact = exact ? 1 : 0;
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int e = 0;
@@ -439,7 +457,7 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   if (count == 0) return HTR_OK;
   if (!qweight_list || !scales_list || !su_list || !sv_list) return HTR_ERR_NULL;
   const int m = mt * 16, n = nt * 16, rbp = m / 128;
-  if ((long long)count * rbp > kCounterBytes / 4) return HTR_ERR_TOO_LARGE;
+  if ((long long)count * rbp > kDoneCounter) return HTR_ERR_TOO_LARGE;
   if (!aligned16(workspace)) return HTR_ERR_ALIGNMENT;
   Plan pl;
   const int rc = make_plan(1, m, n, K, &pl);
@@ -488,7 +506,9 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   p.g_yrow_bytes = (long long)m * esz;
   p.peer_offset = 0;
   for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
+  for (int i = 0; i < 8; ++i) p.peer_flag[i] = nullptr;
   p.wblocks = 0;
+  p.exact = 0;
   p.group = count;
   p.rb_per_problem = rbp;
   p.g_x = x_list;

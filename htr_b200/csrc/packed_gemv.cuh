@@ -43,6 +43,8 @@ constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kStageBlocks = 8;                  // 128-column blocks of activations staged at a time
 constexpr int kStageCols = kStageBlocks * 128;   // 1024 activations per row
 constexpr int kCounterBytes = 1 << 16;           // arrival counters at the start of the workspace (16384 row blocks)
+constexpr int kDoneCounter = kCounterBytes / 4 - 1;   // the last one counts the finished row blocks of a signalling launch
+
 
 struct GemvParams {
   const void* x;
@@ -63,6 +65,8 @@ struct GemvParams {
   int cg_quot, cg_rem;   // split form: cg / split and cg % split (the first cg_rem parts of a row block hold one unit more)
   int slots;        // partial slots per row block
   int wblocks;      // warp-MMA kernel only: 128-column blocks of activations staged at a time
+  int exact;        // warp-MMA kernel only: 1 = one scale per activation row and 64-bit integer sums throughout (the partial sums in
+                    // `part` are then 64-bit: twice the bytes); results are independent of the launch decomposition
   int independent;  // 1: x, bias and y are untouched by the preceding kernel of the stream (wait only before publishing)
   int n_in;         // columns present in x (row stride of x); columns n_in .. n-1 of the stored weight see zeros
   int m_out;        // rows written to y (row stride of y, length of bias); rows m_out .. m-1 of the stored weight are dropped
@@ -78,6 +82,10 @@ struct GemvParams {
   void* peer_y[8];
   int npeer;
   long long peer_offset;
+  // Delivery signal of the peer form: when peer_flag[0] is set, the thread block that finishes the launch's last row block adds 1
+  // to the word peer_flag[pe] of every peer (system scope, after a system-wide fence): "this rank's rows of this call are in your
+  // buffer".  The launch-wide count of finished row blocks lives in the last counter of the workspace (zero between launches).
+  unsigned* peer_flag[8];
   // Grouped form (experts of a mixture-of-experts layer): group > 0 problems of identical shape, one activation row each;
   // the per-problem tensors come from device arrays of device pointers, row blocks are numbered problem-major.  A problem whose
   // weight pointer is null is skipped (its output is left untouched).
@@ -96,6 +104,19 @@ struct GemvParams {
   int g_xdiv;
   long long g_xrow_bytes, g_yrow_bytes;
 };
+
+// Called by every thread of the block that has just stored the output rows of a row block into the peers' buffers.
+__device__ __forceinline__ void signal_peers_when_last(const GemvParams& p, int* counters, int row_blocks) {
+  __syncthreads();                                   // the stores of every warp are issued
+  if (threadIdx.x == 0) {
+    __threadfence_system();                          // ... and ordered before the count (and the flags) for every GPU
+    if (atomicAdd(counters + kDoneCounter, 1) == row_blocks - 1) {
+      counters[kDoneCounter] = 0;
+#pragma unroll 1
+      for (int pe = 0; pe < p.npeer; ++pe) atomicAdd_system(p.peer_flag[pe], 1u);
+    }
+  }
+}
 
 // four consecutive activations of row r at column col (a multiple of 4); columns at or beyond n_in (a multiple of 4) read as zero
 __device__ __forceinline__ float4 load_x(const void* x, int r, int col, int n_in, int dtype) {
@@ -509,6 +530,7 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
         for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);
       }
     }
+    if (finish && p.npeer > 0 && p.peer_flag[0] != nullptr) signal_peers_when_last(p, p.counters, p.mt >> 3);
     if (cgi == CG) { cgi = 0; ++rb; }
     if (u < u_end) {
       // the next row block of the range: the ring has run empty (every copy group issued for the old block has been consumed);

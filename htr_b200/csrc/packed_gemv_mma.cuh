@@ -98,55 +98,22 @@ __device__ __forceinline__ void mma_lane_unit(const uint32_t* __restrict__ tile,
   uint32_t V[K + 1];
   read_unit_words<K>(tile, g, V);
   uint32_t s[32];
-#ifdef HTR_ABL_NOEXTRACT
-#pragma unroll
-  for (int i = 0; i < 32; ++i) s[i] = V[i % (K + 1)] + i;
-#else
   unit_states<K>(V, s);
-#endif
 #pragma unroll
   for (int j4 = 0; j4 < 4; ++j4) {
-#ifdef HTR_ABL_NOB
-    const uint4 b = make_uint4(baddr, baddr + 1, baddr + 2, baddr + 3);
-#else
     const uint4 b = lds128(baddr + j4 * (NB * 64));
-#endif
 #pragma unroll
     for (int jj = 0; jj < 2; ++jj) {
       const int col = 4 * j4 + 2 * jj;
-#ifdef HTR_ABL_NOIMAD
-      const uint32_t a0 = s[col], a1 = s[16 + col], a2 = s[col + 1], a3 = s[17 + col];
-#else
       const uint32_t a0 = s[col] * kGenMul + kGenAdd, a1 = s[16 + col] * kGenMul + kGenAdd;
       const uint32_t a2 = s[col + 1] * kGenMul + kGenAdd, a3 = s[17 + col] * kGenMul + kGenAdd;
-#endif
-#ifdef HTR_ABL_NOMMA
-      d[jj][0] ^= a0 ^ a1 ^ (jj ? b.z : b.x); d[jj][1] ^= a2 ^ a3 ^ (jj ? b.w : b.y);
-#else
       mma_u8s8(d[jj], a0, a1, a2, a3, jj ? b.z : b.x, jj ? b.w : b.y);
-#endif
     }
   }
 }
 
-#ifdef HTR_ABL_TRACE
-static __device__ unsigned long long htr_trace_buf[2048 * 16];
-__device__ __forceinline__ void trace_stamp(int slot) {
-  if (threadIdx.x == 0 && blockIdx.x < 2048) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    htr_trace_buf[blockIdx.x * 16 + slot] = t;
-  }
-}
-#define TR(slot) trace_stamp(slot)
-#else
-#define TR(slot)
-#endif
-#ifndef HTR_ABL_CTAS
-#define HTR_ABL_CTAS 3
-#endif
 template <int K, int NB>
-__global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kGemvThreads, 3) packed_gemv_mma_kernel(const GemvParams p) {
   extern __shared__ __align__(128) unsigned char dyn_smem[];
   constexpr int kStride = MmaTileStride<K>::value, kTileBytes = 32 * K;
   constexpr int kStageBytes = MmaRing<K>::stage_bytes, kStages = MmaStages<K>::value, kDepth = kStages - 1;
@@ -161,8 +128,8 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
   __shared__ float s_row_inv[kMmaRows];
   __shared__ float s_ss[kGemvWarps];
   __shared__ __align__(16) float ytil[kMmaRows * 128];
+  __shared__ unsigned s_rowmax[kMmaRows];                // exact form: float bits of the bound of every transformed activation row
 
-  TR(0);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, c = lane & 3;               // consumer roles: row pair of the strip, tile column of the unit
   const int P = (NB == 8 && p.rows > 2) ? 2 : 4;       // byte planes per activation
@@ -233,9 +200,7 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
   const bool first_item = warp < p.rows * win.nblk;
   const int first_r = warp / win.nblk, first_hb = win.hb0 + warp - first_r * win.nblk;
   if (p.independent && p.prologue != 1 && first_item) x_first = load_item(first_r, first_hb);
-  TR(12);
   issue(0);
-  TR(13);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   bool predecessor_done = false;
   if (!p.independent) {
@@ -245,7 +210,6 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
   }
 #pragma unroll
   for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
-  TR(1);
   if (p.prologue == 1) {
     for (int r = 0; r < p.rows; ++r) {
       float ss = 0.f;
@@ -268,7 +232,32 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
     if (first_item) x_first = load_item(first_r, first_hb);
   }
 
+  // Exact form (p.exact): one power-of-two scale per activation row for the whole launch, so that every window's integers lie
+  // on one grid and all sums -- across windows, across thread blocks -- stay in 64-bit integers.  The scale comes from a bound
+  // that needs no transform: |xt_j| <= sqrt(128) max_i |x_i| < 2^4.5 max|x|.  Every CTA scans the row (a few KB from L2).
+  const bool exact = p.exact != 0;
+  if (exact) {
+    for (int r = 0; r < p.rows; ++r) {
+      unsigned mx = 0u;
+      for (int e = tid; e < (n >> 2); e += kGemvThreads) {
+        const float4 v = load_x(p.x, r, 4 * e, p.n_in, p.dtype);
+        mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(__float_as_uint(v.y) & 0x7FFFFFFFu,
+                 max(__float_as_uint(v.z) & 0x7FFFFFFFu, __float_as_uint(v.w) & 0x7FFFFFFFu)));   // NaN and Inf patterns compare largest
+      }
+      mx = __reduce_max_sync(kFullWarp, mx);
+      if (lane == 0) s_ss[warp] = __uint_as_float(mx);
+      __syncthreads();
+      if (tid == 0) {
+        unsigned all = 0u;
+        for (int k = 0; k < kGemvWarps; ++k) all = max(all, __float_as_uint(s_ss[k]));
+        // four binades up covers the factor sqrt(128) (and the part of a binade above the leading bit)
+        s_rowmax[r] = all >= 0x7F800000u ? 0x7FC00000u : min(all + (4u << 23), 0x7F000000u);
+      }
+      __syncthreads();
+    }
+  }
   float accf[2] = {0.f, 0.f};                          // rows 2g, 2g+1 of the strip for this lane's activation row, summed over windows
+  long long acci[2] = {0ll, 0ll};                       // the same sums as integers on the row's grid (exact form)
   const uint32_t* my_tiles = ring + (warp * 8 + c) * kStride;
   // with four B columns the lanes 16..31 read what lanes 0..15 read: their B columns (4..7) feed accumulator columns nobody uses
   const uint32_t bwin_addr = (uint32_t)__cvta_generic_to_shared(bwin) + (lane & (NB * 4 - 1)) * 16;
@@ -298,7 +287,6 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
       win = window_at(cgi, u_end - u);
       __syncthreads();                                 // the previous window is consumed and its statistics are read
     }
-    TR(2);
     const int hb0 = win.hb0, nblk = win.nblk, items = p.rows * nblk, seg_cg_end = win.seg_end;
 
     // -- pass 1: transform the activations of the window, note the range of every item.  The first kKeep items of a warp stay in
@@ -330,12 +318,11 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
       note_range(item, v);
     }
     __syncthreads();
-    TR(3);
 
     // -- pass 2: byte planes of every activation, splatted over a word, laid out per reader lane
     auto emit_item = [&](int item, const float (&v)[4]) {
       const int r = item / nblk, hbi = item - r * nblk;
-      const unsigned mb = row_amax(r, nblk);
+      const unsigned mb = exact ? s_rowmax[r] : row_amax(r, nblk);
       int ex = (int)(mb >> 23) - 127;
       ex = ex < -90 ? -90 : ex;
       const float sc = __uint_as_float((unsigned)(8 * P - 3 - ex + 127) << 23);   // max * sc in [2^(8P-3), 2^(8P-2))
@@ -379,7 +366,6 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
       emit_item(item, v);
     }
     __syncthreads();
-    TR(4);
 
     // -- main loop of the window: one 128-column block per trip
     int d[2][4];
@@ -392,9 +378,7 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
       async_wait<kDepth - 1>();                        // the oldest copy group (this trip) has landed
       __syncwarp();                                    // ... for every lane; and every lane is done with the previous slot
       const uint32_t* tiles = reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(my_tiles) + stage_bytes);
-#ifndef HTR_ABL_NOREFILL
-      issue(refill_bytes);
-#endif
+      issue(refill_bytes);                             // refill the slot that was consumed one trip ago (or never used yet)
       refill_bytes = stage_bytes;
       stage_bytes = (stage_bytes + kStageBytes == kStages * kStageBytes) ? 0 : stage_bytes + kStageBytes;
       if constexpr (decltype(first)::value) mma_lane_unit<K, NB>(tiles, g, baddr, d);
@@ -411,7 +395,6 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
     if (tail) trip(std::true_type{}, std::false_type{});
     ci += trips;
 
-    TR(5);
     // -- the window's integers leave for float.  Four planes: lane (g, c) holds planes 2 (c & 1), 2 (c & 1) + 1 of activation row
     // c >> 1, the other two sit in the neighbouring lane.  Two planes: both planes of activation row c.
     {
@@ -421,7 +404,7 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
 #pragma unroll
       for (int rr = 0; rr < kMmaRows; ++rr)
         if (rr < p.rows) {                             // (uniform) every lane takes part in the warp-wide reductions
-          const unsigned mrow = row_amax(rr, nblk);
+          const unsigned mrow = exact ? s_rowmax[rr] : row_amax(rr, nblk);
           const long long yrow = row_ysum(rr, nblk);
           if (rr == r) {
             mb = mrow;
@@ -439,9 +422,14 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
       ex = ex < -90 ? -90 : ex;
       const float inv_sc = __uint_as_float((unsigned)(127 - (8 * P - 3) + ex) << 23);   // 1 / sc, a power of two
       if (r < p.rows) {
-        // one rounding (64-bit integer to float); the scaling by a power of two is exact
-        accf[0] += mb < 0x7F800000u ? __ll2float_rn(w0 - 510ll * ysum) * inv_sc : __uint_as_float(0x7FC00000u);
-        accf[1] += mb < 0x7F800000u ? __ll2float_rn(w1 - 510ll * ysum) * inv_sc : __uint_as_float(0x7FC00000u);
+        if (exact) {                                   // integers on the row's grid: summed as they are
+          acci[0] += w0 - 510ll * ysum;
+          acci[1] += w1 - 510ll * ysum;
+        } else {
+          // one rounding (64-bit integer to float); the scaling by a power of two is exact
+          accf[0] += mb < 0x7F800000u ? __ll2float_rn(w0 - 510ll * ysum) * inv_sc : __uint_as_float(0x7FC00000u);
+          accf[1] += mb < 0x7F800000u ? __ll2float_rn(w1 - 510ll * ysum) * inv_sc : __uint_as_float(0x7FC00000u);
+        }
       }
     }
     first_window = false;
@@ -450,12 +438,22 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
     if (cgi < CG && u < u_end) continue;               // same row block, next window
 
     // ---- this CTA's contribution to row block rb is complete
+    long long* ytil_i = reinterpret_cast<long long*>(bwin);     // exact form: [rows][128] 64-bit sums (the window is consumed)
+    if (exact) __syncthreads();                                 // every warp is done reading the B window
     if (P == 2 || (c & 1) == 0) {
       const int r = P == 4 ? (c >> 1) : c;
-      ytil[r * 128 + warp * 16 + 2 * g] = accf[0] * kInvSqrt128;
-      ytil[r * 128 + warp * 16 + 2 * g + 1] = accf[1] * kInvSqrt128;
+      if (exact) {
+        if (r < p.rows) {
+          ytil_i[r * 128 + warp * 16 + 2 * g] = acci[0];
+          ytil_i[r * 128 + warp * 16 + 2 * g + 1] = acci[1];
+        }
+      } else {
+        ytil[r * 128 + warp * 16 + 2 * g] = accf[0] * kInvSqrt128;
+        ytil[r * 128 + warp * 16 + 2 * g + 1] = accf[1] * kInvSqrt128;
+      }
     }
     accf[0] = accf[1] = 0.f;
+    acci[0] = acci[1] = 0ll;
     int contributors;
     if (p.split > 0) {
       contributors = p.split;
@@ -473,45 +471,72 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
       sv_bits = sign_nibble(p.sv, rb * 32 + lane);
       if (p.bias && row0 < p.m_out) bias4 = load_quad(p.bias, row0, p.dtype);
     }
-    TR(6);
     if (!predecessor_done) {
       asm volatile("griddepcontrol.wait;" ::: "memory");
       predecessor_done = true;
     }
     __syncthreads();
-    TR(7);
     bool finish = true;
     const int width = (p.rows <= 1 ? 1 : p.rows <= 2 ? 2 : 4) * 128;
     if (contributors > 1) {
-      float* mine = p.part + ((size_t)rb * p.slots + slot_index) * width;
-      for (int e = tid; e < width; e += kGemvThreads) __stcg(mine + e, ytil[e]);
+      if (exact) {
+        long long* part_i = reinterpret_cast<long long*>(p.part);
+        long long* mine = part_i + ((size_t)rb * p.slots + slot_index) * width;
+        for (int e = tid; e < width; e += kGemvThreads) __stcg(mine + e, ytil_i[e]);
+      } else {
+        float* mine = p.part + ((size_t)rb * p.slots + slot_index) * width;
+        for (int e = tid; e < width; e += kGemvThreads) __stcg(mine + e, ytil[e]);
+      }
       __syncthreads();
-      TR(8);
       if (tid == 0) {
         __threadfence();                               // the partials of the whole CTA (ordered by the barrier) before the arrival
         s_arrival = atomicAdd(p.counters + rb, 1);   // (the finisher reads the partials with loads served by L2, after this atomic)
       }
       __syncthreads();
-      TR(9);
       finish = (s_arrival == contributors - 1);
       if (finish) {
-        const float* slot0 = p.part + (size_t)rb * p.slots * width;
-        for (int e = tid; e < width; e += kGemvThreads) {
-          float sum = 0.f;
-          for (int base = 0; base < contributors; base += 16) {
-            float v[16];
+        if (exact) {
+          const long long* slot0 = reinterpret_cast<const long long*>(p.part) + (size_t)rb * p.slots * width;
+          for (int e = tid; e < width; e += kGemvThreads) {
+            long long sum = 0ll;
+            for (int base = 0; base < contributors; base += 8) {
+              long long v[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = base + j < contributors ? __ldcg(slot0 + (size_t)(base + j) * width + e) : 0.f;
+              for (int j = 0; j < 8; ++j) v[j] = base + j < contributors ? __ldcg(slot0 + (size_t)(base + j) * width + e) : 0ll;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) sum += v[j];
+              for (int j = 0; j < 8; ++j) sum += v[j];
+            }
+            ytil_i[e] = sum;
           }
-          ytil[e] = sum;
+        } else {
+          const float* slot0 = p.part + (size_t)rb * p.slots * width;
+          for (int e = tid; e < width; e += kGemvThreads) {
+            float sum = 0.f;
+            for (int base = 0; base < contributors; base += 16) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = base + j < contributors ? __ldcg(slot0 + (size_t)(base + j) * width + e) : 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sum += v[j];
+            }
+            ytil[e] = sum;
+          }
         }
         if (tid == 0) p.counters[rb] = 0;
       }
       __syncthreads();
     }
-    TR(10);
+    if (exact && finish) {
+      // the sums leave the integer grid here, once, whatever the launch looked like: one rounding, then the exact power of two
+      for (int e = tid; e < width; e += kGemvThreads) {
+        const unsigned mb = s_rowmax[e >> 7];
+        int ex = (int)(mb >> 23) - 127;
+        ex = ex < -90 ? -90 : ex;
+        const float inv_sc = __uint_as_float((unsigned)(127 - (8 * P - 3) + ex) << 23);
+        ytil[e] = mb < 0x7F800000u ? __ll2float_rn(ytil_i[e]) * inv_sc * kInvSqrt128 : __uint_as_float(0x7FC00000u);
+      }
+      __syncthreads();
+    }
     if (finish && warp < p.rows) {
       const int r = warp;
       const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.x)), s23 = __half22float2(*reinterpret_cast<const __half2*>(&sc_raw.y));
@@ -532,10 +557,10 @@ __global__ void __launch_bounds__(kGemvThreads, HTR_ABL_CTAS) packed_gemv_mma_ke
         for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);
       }
     }
+    if (finish && p.npeer > 0 && p.peer_flag[0] != nullptr) signal_peers_when_last(p, p.counters, p.mt >> 3);
     if (cgi == CG) { cgi = 0; ++rb; }                   // (ytil is rewritten only after the barrier that opens the next window)
   }
   async_wait<0>();
-  TR(11);
 }
 
 // host side, defined once per K in packed_gemv_mma_k*.cu

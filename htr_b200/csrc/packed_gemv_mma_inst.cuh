@@ -1,6 +1,4 @@
 // Instantiates the warp-MMA packed GEMV for one stream width; included by packed_gemv_mma_k<K>.cu with HTR_INST_K set.
-#include <cstdlib>
-
 #include "packed_gemv_mma.cuh"
 
 namespace htr {
@@ -39,15 +37,7 @@ static int launch_mma_one(const GemvParams& p, int grid, cudaStream_t stream) {
   return (int)cudaLaunchKernelEx(&cfg, packed_gemv_mma_kernel<K, NB>, p);
 }
 
-// HTR_GEMV_MMA_CTAS in the environment: CTAs per SM the launches are planned for (2 leaves room for larger activation windows)
-static int mma_target_ctas() {
-  static const int value = [] {
-    const char* v = std::getenv("HTR_GEMV_MMA_CTAS");
-    const int t = v ? std::atoi(v) : 3;
-    return t < 1 || t > 4 ? 3 : t;
-  }();
-  return value;
-}
+constexpr int kMmaTargetCtas = 3;                       // CTAs per SM the launches are planned for (registers allow three)
 
 template <int K, int NB>
 static int config_mma_one(int rows, int* ctas_per_sm, int* window_cap) {
@@ -61,7 +51,7 @@ static int config_mma_one(int rows, int* ctas_per_sm, int* window_cap) {
   e = cudaFuncGetAttributes(&fa, packed_gemv_mma_kernel<K, NB>);
   if (e != cudaSuccess) return (int)e;
   const int row_cap = kMmaItems / (rows < 1 ? 1 : rows);
-  for (int target = mma_target_ctas(); target >= 1; --target) {
+  for (int target = kMmaTargetCtas; target >= 1; --target) {
     // every resident CTA costs its static and dynamic shared memory plus 1 KB that the system reserves
     const int budget = per_sm_bytes / target - 1024 - (int)fa.sharedSizeBytes - mma_ring_bytes<K>();
     int cap = budget / (NB * 512);
@@ -93,10 +83,3 @@ int packed_gemv_mma_config<HTR_INST_K>(int rows, int* ctas_per_sm, int* window_c
 
 }  // namespace htr
 
-#ifdef HTR_ABL_TRACE
-#if HTR_INST_K == 4
-extern "C" int htr_trace_read(unsigned long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, htr::htr_trace_buf, sizeof(unsigned long long) * n);
-}
-#endif
-#endif

@@ -200,10 +200,12 @@ def gemm_error_codes():
     return [int(ws[off:off + 4].view(torch.int32).item()) for ws in _GEMM_WS.values()]
 
 
-def linear_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset):
+def linear_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset, flag_ptrs=None):
     """Row-shard form of the GEMV (M <= 8): the result rows [M, m_local] are stored, from inside the kernel, at element
     offset `elem_offset` of every buffer in `peer_ptrs` (device addresses of the gather buffers of all ranks as mapped
-    into this process).  Nothing is returned; the caller orders the ranks (a barrier) before reading the buffers."""
+    into this process).  Nothing is returned.  With `flag_ptrs` (the addresses of this rank's delivery word in every rank's
+    flag array) the kernel also signals the peers when its rows have arrived (htr_linear_peers_signal) and the consumers order
+    themselves with `peer_wait`; without it the caller orders the ranks (a barrier) before reading the buffers."""
     _check(x2, qweight, scales, su, sv, bias)
     M = x2.shape[0]
     if not 1 <= M <= GEMV_MAX_M:
@@ -216,10 +218,24 @@ def linear_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset)
     import ctypes
 
     arr = (ctypes.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
-    rc = _lib.lib.htr_linear_peers(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
-                                   sv.data_ptr(), None if bias is None else bias.data_ptr(), None, arr, len(peer_ptrs), int(elem_offset),
-                                   ws.data_ptr(), ws.numel(), st, _STATE.flags)
+    if flag_ptrs is None:
+        rc = _lib.lib.htr_linear_peers(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
+                                       sv.data_ptr(), None if bias is None else bias.data_ptr(), None, arr, len(peer_ptrs), int(elem_offset),
+                                       ws.data_ptr(), ws.numel(), st, _STATE.flags)
+    else:
+        farr = (ctypes.c_void_p * len(flag_ptrs))(*[int(p) for p in flag_ptrs])
+        rc = _lib.lib.htr_linear_peers_signal(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(),
+                                              su.data_ptr(), sv.data_ptr(), None if bias is None else bias.data_ptr(), arr, farr,
+                                              len(peer_ptrs), int(elem_offset), ws.data_ptr(), ws.numel(), st, _STATE.flags)
     _lib.check(rc, "htr_linear_peers")
+
+
+def peer_wait(flags, epoch, nranks, status=None, count=1):
+    """Consumer side of the delivery flags (htr_peer_wait): wait, on the current stream, until every rank has delivered `count`
+    more times into this GPU's buffer.  flags: int32 CUDA tensor [nranks] (this GPU's words), epoch / status: int32 CUDA tensors [1]."""
+    st = torch.cuda.current_stream(flags.device).cuda_stream
+    rc = _lib.lib.htr_peer_wait(flags.data_ptr(), epoch.data_ptr(), int(nranks), int(count), None if status is None else status.data_ptr(), st)
+    _lib.check(rc, "htr_peer_wait")
 
 
 def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K, dtype):
@@ -270,6 +286,21 @@ class independent_inputs:
     def __enter__(self):
         self._old = _STATE.flags
         _STATE.flags = self._old | _lib.INPUT_INDEPENDENT
+        return self
+
+    def __exit__(self, *exc):
+        _STATE.flags = self._old
+        return False
+
+
+class exact_sums:
+    """Context manager: inside it, packed linears of up to four rows run on the kernel that accumulates in exact integers
+    (HTR_LINEAR_EXACT_SUMS), whose results do not depend on the launch decomposition: row shards of a linear then reproduce the
+    unsharded result bit for bit.  Calls the integer kernel cannot serve are unaffected."""
+
+    def __enter__(self):
+        self._old = _STATE.flags
+        _STATE.flags = self._old | _lib.EXACT_SUMS
         return self
 
     def __exit__(self, *exc):

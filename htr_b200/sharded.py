@@ -20,6 +20,14 @@ import torch
 import torch.distributed as dist
 
 
+# How the ranks order themselves after peer stores: "barrier" = the producer kernel ends, then one cross-rank barrier kernel of
+# torch's symmetric memory (signal + wait on every peer); "flags" = the producer kernel raises delivery flags itself and the
+# consumer runs a bounded wait (htr_peer_wait).  Measured on 2 B200s the barrier form is the faster one (the flags need a
+# system-wide fence in every finishing thread block, which drains the SM's memory pipeline): 85.8 against 93.2 us for the
+# 151936x4096 head at batch 1, 3632 against 2910 GB/s on the weak-scaled MLP sweep.
+PEER_ORDER = "barrier"
+
+
 def row_block_partition(m, world):
     """Split m/128 row blocks into `world` contiguous runs of equal padded length.
     Returns (blocks_per_rank, [(first_block, real_blocks), ...]).  151936 rows = 1187 blocks over 8 ranks -> 149 per rank,
@@ -85,10 +93,12 @@ def all_gather_rows(y_local, group=None):
 
 class PeerGather:
     """Gather buffers in symmetric memory: every rank maps every rank's buffer, so a kernel can store its output rows
-    straight into all of them over NVLink (htr_linear_peers) and no collective kernel runs.  `barrier()` orders the
-    ranks on the current stream: after it, every rank's rows are in this rank's buffer.
+    straight into all of them over NVLink (htr_linear_peers) and no collective kernel runs.  The ranks then order themselves
+    with `barrier()` (one small kernel across the ranks) or, with delivery flags (htr_linear_peers_signal: the producer kernel
+    raises this rank's word in every rank's flag array), with `wait()`, a bounded wait on the current stream.
 
-    Two alternating buffers let a fast rank start the next call while a slow one still reads the previous result."""
+    Two alternating buffers: a rank that is one call ahead writes the half that its peers have finished reading (a rank consumes
+    the result of call i - 1, on its stream, before it launches call i + 1)."""
 
     def __init__(self, world, rank, max_rows, rows_per_rank, dtype, device, group=None):
         import os
@@ -96,10 +106,19 @@ class PeerGather:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer stores only, no NVLink multicast objects
         import torch.distributed._symmetric_memory as symm_mem
 
+        grp = group if group is not None else dist.group.WORLD
         self.world, self.rank, self.max_rows, self.rows_per_rank = world, rank, max_rows, rows_per_rank
         self.buf = symm_mem.empty((2, world, max_rows, rows_per_rank), dtype=dtype, device=device)
-        self.hdl = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        self.hdl = symm_mem.rendezvous(self.buf, grp)
         self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)          # word r: deliveries of rank r into this GPU's buffer
+        self.flags.zero_()
+        self.flag_hdl = symm_mem.rendezvous(self.flags, grp)
+        self.flag_ptrs = [int(p) + 4 * rank for p in self.flag_hdl.buffer_ptrs]     # this rank's word in every rank's array
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)              # bit r: rank r missed a bounded wait
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)                                                      # every rank's flags are zero before anyone signals
         self.flip = 0
         self.esize = self.buf.element_size()
 
@@ -108,8 +127,20 @@ class PeerGather:
         half = self.flip * self.world * self.max_rows * self.rows_per_rank
         return [p + half * self.esize for p in self.ptrs], self.rank * self.max_rows * self.rows_per_rank
 
+    def wait(self, count=1):
+        from . import ops
+
+        ops.peer_wait(self.flags, self.epoch, self.world, self.status, count)
+
     def barrier(self):
         self.hdl.barrier(channel=0)
+
+    def check(self):
+        """Host-side check (synchronises): raises if a bounded wait ran out since the last check."""
+        missed = int(self.status.item())
+        if missed:
+            self.status.zero_()
+            raise RuntimeError(f"peer delivery wait timed out for ranks {[r for r in range(self.world) if missed >> r & 1]}")
 
     def result(self, rows):
         out = self.buf[self.flip, :, :rows, :]
@@ -121,7 +152,8 @@ class RowShardedLinear:
     """y = x @ W^T (+bias) with W's rows dealt to the ranks of `group`; every rank gets the full [.., m] result.
 
     gather="nccl": all-gather of the local outputs.  gather="peer": the GEMV's epilogue stores its rows into every rank's
-    gather buffer itself (up to 8 activation rows; larger batches fall back to the all-gather)."""
+    gather buffer itself and raises a delivery flag there (up to 4 activation rows; larger batches run the tensor-core GEMM
+    locally and all-gather its output)."""
 
     def __init__(self, qweight, scales, su, sv, bias=None, group=None, device=None, linear_fn=None, gather="nccl", dtype=torch.bfloat16):
         self.group = group
@@ -133,26 +165,44 @@ class RowShardedLinear:
         self.qweight, self.scales, self.sv = q.to(dev), s.to(dev), v.to(dev)
         self.su = su.to(dev).contiguous()
         self.bias = None if b is None else b.to(dev)
+        self._cuda_operator = linear_fn is None
         self.linear_fn = linear_fn or _default_linear()
         self.peer = None
         if gather == "peer" and self.world > 1:
             self.peer = PeerGather(self.world, self.rank, 8, self.qweight.shape[0] * 16, dtype, dev, group)
 
+    def _exact(self):
+        """Row shards must reproduce the unsharded rows whatever the shard count: up to four rows run on the integer-exact kernel."""
+        if self._cuda_operator:
+            from . import ops
+
+            return ops.exact_sums()
+        import contextlib
+
+        return contextlib.nullcontext()
+
     def local(self, x):
         """This rank's slice of the output, [.., rows_per_rank] (padding rows are zero)."""
         bias = None if self.bias is None else self.bias.to(x.dtype)
-        return self.linear_fn(x, self.qweight, self.scales, self.su, self.sv, bias)
+        with self._exact():
+            return self.linear_fn(x, self.qweight, self.scales, self.su, self.sv, bias)
 
     def __call__(self, x):
         lead = x.shape[:-1]
         x2 = x.reshape(-1, self.n)
-        if self.peer is not None and 1 <= x2.shape[0] <= 8 and x2.dtype == self.peer.buf.dtype:
+        if self.peer is not None and 1 <= x2.shape[0] <= 4 and x2.dtype == self.peer.buf.dtype:
             from . import ops
 
             ptrs, off = self.peer.target()
             bias = None if self.bias is None else self.bias.to(x2.dtype)
-            ops.linear_into_peers(x2.contiguous(), self.qweight, self.scales, self.su, self.sv, bias, ptrs, off)
-            self.peer.barrier()
+            flags = PEER_ORDER == "flags"
+            with ops.exact_sums():
+                ops.linear_into_peers(x2.contiguous(), self.qweight, self.scales, self.su, self.sv, bias, ptrs, off,
+                                      self.peer.flag_ptrs if flags else None)
+            if flags:
+                self.peer.wait()
+            else:
+                self.peer.barrier()
             g = self.peer.result(x2.shape[0])                                # [world, M, rows_per_rank]
             rows = x2.shape[0]
         else:
@@ -190,6 +240,7 @@ class ExpertParallelMoE:
         self.local = {e: dict(gate_up=put(experts[e]["gate_up"]), down=put(experts[e]["down"])) for e in range(first, first + count)}
         self.linear_fn = linear_fn or _default_linear()
         self._tables = None
+        self._peer = None
 
     def _address_tables(self, dev):
         """int64 device tensors [all experts] with the addresses of each expert's wire tensors (for the grouped kernel);
@@ -201,11 +252,11 @@ class ExpertParallelMoE:
             self._tables = {w: tuple(col(w, i) for i in range(4)) for w in ("gate_up", "down")}
         return self._tables
 
-    def partial_grouped(self, x, topk_ids, topk_w):
-        """The same contribution with two routed launches over all (token, slot) pairs: gate_up reads token row pair // k, down
-        reads the pair's [gate | up] row and applies SwiGLU while staging it (bf16; other dtypes use a separate activation step).
-        Routing stays on the device (no host round trip, capturable in a CUDA graph); pairs routed to another rank's experts are
-        skipped by the kernel (null weight address) and contribute zero here."""
+    def routed_outputs(self, x, topk_ids):
+        """Expert outputs of every (token, slot) pair owned by this rank, [T * k, h] in x.dtype, with two routed launches over all
+        pairs: gate_up reads token row pair // k, down reads the pair's [gate | up] row and applies SwiGLU while staging it (bf16;
+        other dtypes use a separate activation step).  Routing stays on the device (no host round trip, capturable in a CUDA
+        graph); pairs routed to another rank's experts are skipped by the kernel (null weight address) and stay zero."""
         from . import ops
 
         T, hdim = x.shape
@@ -228,7 +279,66 @@ class ExpertParallelMoE:
             inter = mt_gu * 8
             act = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).contiguous()
             ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, out=dn)
-        return torch.einsum("tkh,tk->th", dn.view(T, k, -1).float(), topk_w.to(device=dev, dtype=torch.float32))
+        return dn
+
+    def partial_grouped(self, x, topk_ids, topk_w):
+        """Contribution of this rank's experts, float32 [T, h]: the routed launches + the gate-weighted sum over the slots."""
+        T, k = topk_ids.shape
+        dn = self.routed_outputs(x, topk_ids)
+        return torch.einsum("tkh,tk->th", dn.view(T, k, -1).float(), topk_w.to(device=x.device, dtype=torch.float32))
+
+    def _peer_combine(self, dn, topk_w, T, k, hdim, dtype):
+        """Combine over the ranks without a collective: the gate-weighted sum of this rank's pairs is stored into every rank's
+        buffer (htr_moe_combine_peers: plain peer stores), the ranks order themselves (PEER_ORDER) and every rank adds the parts in
+        rank order (htr_rank_sum), so all ranks hold the same bits."""
+        import ctypes
+
+        from . import _lib, ops
+
+        dev = dn.device
+        pc = self._peer
+        if pc is None:
+            import os
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+
+            grp = self.group if self.group is not None else dist.group.WORLD
+            pc = {"max_t": 64}
+            pc["buf"] = symm_mem.empty((2, self.world, pc["max_t"], hdim), dtype=torch.float32, device=dev)
+            hdl = symm_mem.rendezvous(pc["buf"], grp)
+            pc["flags"] = symm_mem.empty(64, dtype=torch.int32, device=dev)
+            pc["flags"].zero_()
+            fh = symm_mem.rendezvous(pc["flags"], grp)
+            pc["hdls"] = (hdl, fh)
+            half_bytes = self.world * pc["max_t"] * hdim * 4
+            pc["out_ptrs"] = [torch.tensor([int(p) + hf * half_bytes for p in hdl.buffer_ptrs], dtype=torch.int64, device=dev) for hf in (0, 1)]
+            pc["flag_ptrs"] = torch.tensor([int(p) + 4 * self.rank for p in fh.buffer_ptrs], dtype=torch.int64, device=dev)
+            pc["epoch"] = torch.zeros(1, dtype=torch.int32, device=dev)
+            pc["status"] = torch.zeros(1, dtype=torch.int32, device=dev)
+            pc["done"] = torch.zeros(1, dtype=torch.int32, device=dev)
+            pc["flip"] = 0
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=grp)
+            self._peer = pc
+        half = pc["flip"]
+        pc["flip"] ^= 1
+        st = torch.cuda.current_stream(dev).cuda_stream
+        code = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}[dtype]
+        gates = topk_w.to(device=dev, dtype=torch.float32).contiguous()
+        flags = PEER_ORDER == "flags"
+        rc = _lib.lib.htr_moe_combine_peers(dn.data_ptr(), code, gates.data_ptr(), T, k, hdim, pc["out_ptrs"][half].data_ptr(), self.world,
+                                            self.rank * pc["max_t"] * hdim, pc["flag_ptrs"].data_ptr() if flags else None,
+                                            pc["done"].data_ptr() if flags else None, st)
+        _lib.check(rc, "htr_moe_combine_peers")
+        if flags:
+            ops.peer_wait(pc["flags"], pc["epoch"], self.world, pc["status"])
+        else:
+            pc["hdls"][0].barrier(channel=0)
+        out = torch.empty(T, hdim, dtype=dtype, device=dev)
+        rc = _lib.lib.htr_rank_sum(pc["buf"][half].data_ptr(), self.world, pc["max_t"] * hdim, T, hdim, out.data_ptr(), code, st)
+        _lib.check(rc, "htr_rank_sum")
+        return out
 
     def partial(self, x, topk_ids, topk_w):
         """Contribution of this rank's experts, float32 [T, h].  Routing is resolved on the host."""
@@ -248,8 +358,15 @@ class ExpertParallelMoE:
             out.index_add_(0, tok, d.float() * w[:, None])
         return out
 
-    def __call__(self, x, topk_ids, topk_w, grouped=None):
+    def __call__(self, x, topk_ids, topk_w, grouped=None, combine=None):
+        """combine: "peer" = peer stores + delivery flags + rank-ordered add (CUDA, grouped form, up to 64 tokens),
+        "nccl" = all-gather of the float32 parts + rank-ordered add; default: "peer" where it applies."""
         use_grouped = (x.is_cuda and self.count > 0) if grouped is None else grouped
+        T, hdim = x.shape
+        if (self.world > 1 and use_grouped and x.is_cuda and T <= 64 and combine in (None, "peer") and self.num_experts >= self.world
+                and dist.get_backend(self.group) == "nccl"):
+            dn = self.routed_outputs(x, topk_ids)
+            return self._peer_combine(dn, topk_w, T, topk_ids.shape[1], hdim, x.dtype)
         part = self.partial_grouped(x, topk_ids, topk_w) if use_grouped else self.partial(x, topk_ids, topk_w)
         if self.world == 1:
             return part.to(x.dtype)

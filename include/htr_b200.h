@@ -78,6 +78,11 @@ int htr_linear(const void* x, int dtype, int M, const void* qweight, int mt, int
  * packed words, but waits for its predecessor before reading x.  (No counterpart in the reference, whose
  * launches serialise on the stream, htr_kernels.cu:920.) */
 #define HTR_LINEAR_INPUT_INDEPENDENT 1u
+/* HTR_LINEAR_EXACT_SUMS asks for the kernel that accumulates in exact integers (the warp-MMA GEMV: up to two rows of any type,
+ * three or four bf16 rows; other calls ignore the flag).  Its results do not depend on how the launch is cut into thread blocks,
+ * so a row shard of a linear reproduces the rows of the unsharded result bit for bit whatever the number of shards.  At one row it
+ * costs a few per cent against the default kernel, whose float32 sums follow the launch decomposition. */
+#define HTR_LINEAR_EXACT_SUMS 2u
 int htr_linear_ex(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
                   const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
                   size_t workspace_bytes, htr_stream_t stream, unsigned flags);
@@ -92,6 +97,31 @@ int htr_linear_peers(const void* x, int dtype, int M, const void* qweight, int m
                      const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y /* may be NULL when npeer > 0 */,
                      void* const* peer_y, int npeer, int64_t peer_offset, void* workspace, size_t workspace_bytes,
                      htr_stream_t stream, unsigned flags);
+
+/* htr_linear_peers that also tells the peers when this rank's rows have arrived, so that no barrier across the ranks is needed:
+ * peer_flags[i] is the address, as mapped into this process, of the 32-bit word "this rank has delivered" in the memory of the
+ * GPU that owns peer_y[i].  The thread block that finishes the launch's last row block adds 1 to each of them (system scope,
+ * after a system-wide fence behind the stores).  The consumer orders itself with htr_peer_wait on its own stream.  Uses the last
+ * arrival counter of the workspace as the launch-wide count (m / 128 must stay below 16383).  A rank must have consumed the
+ * result of call i - 1 (on its stream) before it launches call i + 1 into the same buffer: callers alternate two buffers.
+ * (No counterpart in the reference.) */
+int htr_linear_peers_signal(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+                            const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* const* peer_y,
+                            unsigned* const* peer_flags, int npeer, int64_t peer_offset, void* workspace, size_t workspace_bytes,
+                            htr_stream_t stream, unsigned flags);
+/* Consumer side of the delivery flags: one small kernel on `stream` that waits until each of flags[0..nranks) (this GPU's words,
+ * one per producing rank) has reached *epoch + count (count deliveries per rank since the last wait), then stores that number to *epoch (both in device memory: the sequence
+ * survives CUDA-graph replay).  The wait is bounded (about two seconds); a producer that has not delivered by then gets its bit
+ * set in *status (device int, may be NULL) and the kernel returns: the buffer then holds stale rows. */
+int htr_peer_wait(const unsigned* flags, unsigned* epoch, int nranks, int count, int* status, htr_stream_t stream);
+/* Combine step of an expert-parallel mixture-of-experts layer without a collective: part[t, :] = sum_j gates[t, j] *
+ * dn[t * top_k + j, :] (float32) is stored into every peer's buffer at float offset slot_offset (+ t * hidden), with the same
+ * delivery signal as above when peer_flag is given (done_counter: a zeroed device int of this rank); htr_rank_sum then adds the
+ * ranks' parts in rank order (every rank obtains the same bits) and casts to the output type. */
+int htr_moe_combine_peers(const void* dn, int dtype, const float* gates, int tokens, int top_k, int hidden, float* const* peer_out,
+                          int npeer, int64_t slot_offset, unsigned* const* peer_flag /* may be NULL */, int* done_counter,
+                          htr_stream_t stream);
+int htr_rank_sum(const float* buf, int world, int64_t rank_stride, int tokens, int hidden, void* out, int dtype, htr_stream_t stream);
 
 /* Grouped form of htr_linear: `count` packed linears of one shape [m, n] and width K, one activation row each, in ONE launch
  * (the experts hit by the tokens of a mixture-of-experts step).  Every list is a DEVICE array of `count` device pointers

@@ -180,3 +180,27 @@ def test_plan_and_workspace_cover_both_kernels(dev):
         rows_t = 1 if M <= 1 else 2 if M <= 2 else 4
         assert need >= _lib.lib.htr_linear_counter_bytes(m) + (m // 128) * slots.value * rows_t * 128 * 4
         assert 1 <= grid.value <= 3 * torch.cuda.get_device_properties(dev).multi_processor_count
+
+
+@pytest.mark.parametrize("K,m,n", ((4, 20480, 4096), (3, 4096, 12288), (2, 2560, 1024), (5, 37888, 2048)))
+@pytest.mark.parametrize("M", (1, 2))
+def test_exact_sums_do_not_depend_on_the_launch_decomposition(coracle, dev, K, m, n, M):
+    """HTR_LINEAR_EXACT_SUMS (ops.exact_sums): one scale per activation row and 64-bit integer sums across windows and thread
+    blocks.  A run of row blocks cut out of the weight is launched with another grid and other column splits, and must still
+    reproduce its rows of the full result bit for bit (what row sharding over several GPUs relies on); accuracy as usual."""
+    from htr_b200 import ops, wire
+
+    qw, sc, su, sv = wire.random_packed(m, n, K, 4000 + K)
+    args = [t.to(dev) for t in (qw, sc, su, sv)]
+    x = torch.randn(M, n, generator=torch.Generator().manual_seed(K + M))
+    x[0, 5] = 37.0                                               # an outlier: the row scale follows a bound on the whole row
+    with ops.exact_sums():
+        y = ops.linear(x.to(dev), *args)
+        yb = ops.linear(x.bfloat16().to(dev), *args)
+        for lo, hi in ((0, 128), (m // 128 // 3 * 128, m // 128 // 3 * 128 + 896), (m - 384, m)):
+            part = [args[0][lo // 16:hi // 16].contiguous(), args[1][lo:hi].contiguous(), args[2], args[3][lo // 8:hi // 8].contiguous()]
+            assert torch.equal(ops.linear(x.to(dev), *part), y[:, lo:hi])
+            assert torch.equal(ops.linear(x.bfloat16().to(dev), *part), yb[:, lo:hi])
+    ref = coracle.linear(x.numpy(), qw.numpy(), sc.numpy(), su.numpy(), sv.numpy())
+    assert rel(y.cpu().numpy(), ref) <= 1e-5
+    check_bf16(yb, coracle.linear(x.bfloat16().float().numpy(), qw.numpy(), sc.numpy(), su.numpy(), sv.numpy()))

@@ -159,16 +159,33 @@ def _nccl_worker(rank, world, port, q):
         from htr_b200.sharded import RowShardedLinear
 
         qw, sc, su, sv = wire.random_packed(128 * 11, 1024, 4, seed=8)      # 11 row blocks over 2 ranks: 6 + (5 real, 1 padding)
-        x = torch.randn(3, 1024, generator=torch.Generator().manual_seed(9)).bfloat16().to(dev)
+        full_w = [t.to(dev) for t in (qw, sc, su, sv)]
+        x = torch.randn(2, 1024, generator=torch.Generator().manual_seed(9)).bfloat16().to(dev)
+        # up to two rows run on the integer-exact kernel, whose sums do not depend on the launch decomposition: the gathered result
+        # is the single-GPU result (under the same flag) bit for bit
         y = RowShardedLinear(qw, sc, su, sv, device=dev)(x)
-        full = ops.linear(x, qw.to(dev), sc.to(dev), su.to(dev), sv.to(dev))
+        with ops.exact_sums():
+            full = ops.linear(x, *full_w)
         ok = bool(torch.equal(y, full))
-        # the same through peer stores from the kernel epilogue (symmetric memory, no collective kernel), three calls in a row
+        # the same through peer stores from the kernel epilogue (symmetric memory, delivery flags, no collective kernel), three
+        # calls in a row, one and two rows
+        from htr_b200 import sharded as sharded_mod
+
         peer = RowShardedLinear(qw, sc, su, sv, device=dev, gather="peer")
-        for i in range(3):
-            xi = (x * (i + 1)).contiguous()
-            want = ops.linear(xi, qw.to(dev), sc.to(dev), su.to(dev), sv.to(dev))
-            ok = ok and bool(torch.equal(peer(xi), want))
+        for order in ("barrier", "flags"):                                   # both ways of ordering the ranks after the peer stores
+            sharded_mod.PEER_ORDER = order
+            for i in range(3):
+                xi = (x[:1 + i % 2] * (i + 1)).contiguous()
+                with ops.exact_sums():
+                    want = ops.linear(xi, *full_w)
+                ok = ok and bool(torch.equal(peer(xi), want))
+        peer.peer.check()                                                    # no bounded wait ran out
+        sharded_mod.PEER_ORDER = "barrier"
+        # three rows (float32 sums per window): within bf16 rounding of the single-GPU result; eight rows: local GEMM + all-gather
+        for rows in (3, 8):
+            xr = torch.randn(rows, 1024, generator=torch.Generator().manual_seed(rows)).bfloat16().to(dev)
+            got, want = peer(xr).float(), ops.linear(xr, *full_w).float()
+            ok = ok and float((got - want).norm() / want.norm()) <= 4e-3
         # expert-parallel MoE, 8 experts over the two ranks: device-routed grouped launches (pairs of the other rank's experts are
         # skipped by the kernel) against host routing and against the CPU reference
         from htr_b200.sharded import ExpertParallelMoE
@@ -179,6 +196,15 @@ def _nccl_worker(rank, world, port, q):
         y_loop = moe(xm.to(dev), ids, w, grouped=False).float().cpu()
         want = _moe_reference(experts, xm, ids, w, _oracle_linear())
         ok = ok and float((y_grp - want).norm() / want.norm()) <= 1e-5 and float((y_loop - want).norm() / want.norm()) <= 1e-5
+        # the combine by peer stores and delivery flags (the default above) against the all-gather form, and twice more in a row
+        # (the two halves of the buffers alternate)
+        y_nccl = moe(xm.to(dev), ids, w, combine="nccl").float().cpu()
+        ok = ok and float((y_grp - y_nccl).norm() / y_nccl.norm()) <= 1e-6
+        for order in ("barrier", "flags", "barrier"):
+            sharded_mod.PEER_ORDER = order
+            ok = ok and bool(torch.equal(moe(xm.to(dev), ids, w).float().cpu(), y_grp))
+        sharded_mod.PEER_ORDER = "barrier"
+        ok = ok and int(moe._peer["status"].item()) == 0
         torch.cuda.synchronize()
         q.put((rank, ok, tuple(y.shape)))
     finally:
@@ -199,4 +225,75 @@ def test_two_nccl_ranks_match_single_gpu_bit_for_bit():
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    assert all(ok and shape == (3, 128 * 11) for _, ok, shape in res)
+    assert all(ok and shape == (2, 128 * 11) for _, ok, shape in res)
+
+
+@pytest.mark.gpu
+def test_peer_wait_gives_up_and_reports_the_missing_rank():
+    """The consumer's wait for delivery flags is bounded: with a flag that nothing raises, the kernel returns after about two
+    seconds, sets the missing rank's bit in the status word and leaves the context usable."""
+    from htr_b200 import ops
+
+    dev = torch.device("cuda:0")
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)
+    flags[0] = 1                                                            # rank 0 has delivered, rank 1 never does
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.peer_wait(flags, epoch, 2, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0b10 and int(epoch.item()) == 1
+    flags[1] = 2                                                            # both ranks are at call 2 now: the next wait passes at once
+    flags[0] = 2
+    status.zero_()
+    ops.peer_wait(flags, epoch, 2, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(epoch.item()) == 2
+    assert float(torch.ones(4, device=dev).sum()) == 4.0                    # the device still answers
+
+
+def _failing_gloo_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        from htr_b200.sharded import all_gather_rows
+
+        y = torch.full((2, 4), float(rank))
+        all_gather_rows(y)                                                   # one healthy round first
+        if rank == 1:
+            raise RuntimeError("injected failure: this rank leaves before the collective")
+        try:
+            all_gather_rows(y)                                               # the peer never joins: must end with an error, not hang
+            q.put((rank, "returned"))
+        except Exception as e:                                               # noqa: BLE001 - any error from the backend will do
+            q.put((rank, "error: " + type(e).__name__))
+    except RuntimeError as e:
+        q.put((rank, "left: " + str(e)[:40]))
+        q.close()
+        q.join_thread()                                                      # the message is on its way before the process dies
+        os._exit(3)                                                          # leave without tearing the group down, as a crashed rank does
+    finally:
+        if rank == 0:
+            try:
+                dist.destroy_process_group()
+            except Exception:                                                # noqa: BLE001
+                pass
+
+
+def test_a_rank_that_leaves_ends_the_others_collective_with_an_error():
+    """Host-side failure handling of the sharded forms: the gathers are torch.distributed collectives, so a rank that dies
+    between steps surfaces on its peers as an exception from the next collective within the process group's timeout (20 s
+    here) -- never as a hang.  Two gloo ranks on CPU; rank 1 raises before the second all-gather."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_gloo_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=90) for _ in range(2))
+    for p in procs:
+        p.join(timeout=60)
+    assert got[1].startswith("left")
+    assert got[0].startswith("error"), got
+    assert procs[1].exitcode == 3
