@@ -386,15 +386,16 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
     __syncthreads();                                                // the previous users of the staging buffer are done
     const int nblk = hb1 - hb0, items = MT * nblk;
     float4 xv_first = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (warp < items && warp / nblk < p.rows)                       // the first item's loads go out before the copy burst
-      xv_first = fused_x(p, x_ptr, warp / nblk, (hb0 + warp % nblk) * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[warp / nblk] : 1.f);
+    const int first_r = MT == 1 ? 0 : warp / nblk;                  // (one activation row: no divisions in the staging)
+    if (warp < items && first_r < p.rows)                           // the first item's loads go out before the copy burst
+      xv_first = fused_x(p, x_ptr, first_r, (hb0 + warp - first_r * nblk) * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[first_r] : 1.f);
     if (!ring_primed) {
 #pragma unroll
       for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
       ring_primed = true;
     }
     for (int item = warp; item < items; item += kGemvWarps) {
-      const int r = item / nblk, hb = hb0 + item % nblk;
+      const int r = MT == 1 ? 0 : item / nblk, hb = hb0 + item - r * nblk;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       if (r < p.rows) {
         const float4 xv = item == warp ? xv_first : fused_x(p, x_ptr, r, hb * 128 + 4 * lane, p.prologue == 1 ? s_row_inv[r] : 1.f);

@@ -186,8 +186,8 @@ int htr_linear_fused(const void* x, int M, const void* qweight, int mt, int nt, 
  * decoded tiles go straight into the shared-memory operand of tcgen05.mma, accumulators live in TMEM; two launches
  * (activation transform to fp16 hi/lo planes, then the GEMM with the same split reduction and epilogue as the GEMV).
  * The workspace starts with the same zero-initialised counter region as htr_linear's, followed by one status word at
- * htr_linear_gemm_error_offset(): non-zero after a call means a bounded device-side wait expired and the output is
- * invalid.  Stands in for the prefill branch of _linear_impl, dequant_w + F.linear (htr/ops.py:89-93). */
+ * htr_linear_gemm_error_offset(): non-zero after a call means a bounded device-side wait expired; the rows of the
+ * affected 128-row blocks are then written as NaN.  Stands in for the prefill branch of _linear_impl, dequant_w + F.linear (htr/ops.py:89-93). */
 #define HTR_GEMM_MAX_ROWS 256
 #define HTR_GEMM_MAX_ROWS_F32 128 /* float32 activations travel as two fp16 planes: half as many rows per call */
 size_t htr_linear_gemm_workspace_bytes(int M, int m, int n, int K);
