@@ -159,9 +159,10 @@ static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
   // one extra publish + restage, which is only cheap when a CTA owns many units).  Otherwise: flat even ranges.
   const long long flat_grid = cap < pl.units ? cap : pl.units;
   int longest;                                            // units of one row block that a CTA may own
-  if (pl.rbs <= cap && pl.units / flat_grid < 24) {
-    long long s = cap / pl.rbs;
-    if (s > pl.cg) s = pl.cg;
+  long long s = pl.rbs <= cap ? cap / pl.rbs : 0;
+  if (s > pl.cg) s = pl.cg;
+  // (the split form must also fill the GPU: 149 row blocks on 444 slots would leave a third of them empty with two CTAs per block)
+  if (s >= 1 && pl.units / flat_grid < 24 && (5 * pl.rbs * s >= 4 * cap || pl.units / flat_grid < 8)) {
     pl.split = (int)s;
     pl.grid = pl.rbs * pl.split;
     pl.slots = pl.split;
