@@ -182,8 +182,13 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def _time_graph(torch, dist, world, dev, fn, reps):
-    """ms per call of fn(): captured into a CUDA graph when possible, CUDA events, barrier on both sides, max over ranks."""
+def _time_graph(torch, dist, world, dev, fn, reps, calls=1):
+    """ms per call of fn(): captured into a CUDA graph when possible, CUDA events, barrier on both sides, max over ranks.
+    calls=2 captures two calls in a row per graph: the sharded layers alternate between the two halves of their exchange buffers
+    from call to call, and a replayed graph must hold both halves to keep that ordering."""
+    once = fn
+    if calls > 1:
+        fn = lambda: [once() for _ in range(calls)]     # noqa: E731
     def sync_all():
         torch.cuda.synchronize()
         if world > 1:
@@ -208,7 +213,7 @@ def _time_graph(torch, dist, world, dev, fn, reps):
         run()
     e1.record()
     sync_all()
-    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev, dtype=torch.float64)
+    t = torch.tensor([e0.elapsed_time(e1) / (reps * calls)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t[0])
@@ -249,17 +254,17 @@ def lm_head_record(torch, dist, rank, world, dev, reps):
                     raise RuntimeError("row-sharded LM head differs from the single-GPU result")
                 if M > 1 and not float((ya.float() - yb.float()).norm() / yb.float().norm()) <= 4e-3:
                     raise RuntimeError("row-sharded LM head (batch 8) is not within bf16 rounding of the single-GPU result")
-        t_n = _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps) / copies
-        t_1 = _time_graph(torch, dist, world, dev, lambda: [h(x) for h in single], reps) / copies if world > 1 else t_n
+        t_n = _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps, calls=2) / copies
+        t_1 = _time_graph(torch, dist, world, dev, lambda: [h(x) for h in single], reps, calls=2) / copies if world > 1 else t_n
         out[f"batch{M}"] = {"us": round(1e3 * t_n, 2), "one_gpu_us": round(1e3 * t_1, 2), "speedup": round(t_1 / t_n, 3),
                             "efficiency": round(t_1 / t_n / world, 3), "packed_GBps": round(payload_bytes(m, n, K) / (t_n * 1e-3) / 1e9, 1)}
         if world > 1:
             # where the time goes: the shard's kernel alone (no hand-over), and the other way of ordering the ranks
-            out[f"batch{M}"]["shard_kernel_only_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h.local(x) for h in sharded], reps) / copies, 2)
+            out[f"batch{M}"]["shard_kernel_only_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h.local(x) for h in sharded], reps, calls=2) / copies, 2)
             if M == 1:
                 from htr_b200 import sharded as sharded_mod
                 sharded_mod.PEER_ORDER = "flags"
-                out[f"batch{M}"]["with_delivery_flags_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps) / copies, 2)
+                out[f"batch{M}"]["with_delivery_flags_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps, calls=2) / copies, 2)
                 sharded_mod.PEER_ORDER = "barrier"
     if world > 1:
         out["gather_check"] = "batch 1: bit-identical to the single-GPU result; batch 8: within bf16 rounding (4e-3 norm-relative)"
@@ -281,7 +286,8 @@ def moe_record(torch, dist, rank, world, dev, reps, tokens=(1, 8, 32)):
     moe1 = ExpertParallelMoE(experts, device=dev, group=solo) if world > 1 else moe
     del experts
     out = {"workload": "moe_64x_top8_swiglu_4096_1536_K3",
-           "combine": "peer stores of the gate-weighted parts + one cross-rank barrier + rank-ordered add" if world > 1 else "none"}
+           "combine": ("the down launch stores each pair's row into every rank (peer stores), one cross-rank barrier, the single-GPU weighted sum; "
+                       "bit-identical to the single-GPU layer") if world > 1 else "none"}
     g = torch.Generator().manual_seed(0)
     for T in tokens:
         x = torch.randn(T, h, generator=g).bfloat16().to(dev)
@@ -289,12 +295,10 @@ def moe_record(torch, dist, rank, world, dev, reps, tokens=(1, 8, 32)):
         w = torch.rand(T, 8, generator=g)
         w = (w / w.sum(-1, keepdim=True)).to(dev)
         if world > 1:
-            a, b = moe(x, ids, w).float(), moe1(x, ids, w).float()
-            err = float((a - b).norm() / b.norm())
-            if not err <= 1e-2:
-                raise RuntimeError(f"expert-parallel MoE differs from the single-GPU layer: {err}")
-        t_n = _time_graph(torch, dist, world, dev, lambda: moe(x, ids, w), reps)
-        t_1 = _time_graph(torch, dist, world, dev, lambda: moe1(x, ids, w), reps) if world > 1 else t_n
+            if not torch.equal(moe(x, ids, w), moe1(x, ids, w)):
+                raise RuntimeError("expert-parallel MoE differs from the single-GPU layer")
+        t_n = _time_graph(torch, dist, world, dev, lambda: moe(x, ids, w), reps, calls=2)
+        t_1 = _time_graph(torch, dist, world, dev, lambda: moe1(x, ids, w), reps, calls=2) if world > 1 else t_n
         out[f"tokens{T}"] = {"ms": round(t_n, 4), "one_gpu_ms": round(t_1, 4), "speedup": round(t_1 / t_n, 3)}
     return out
 

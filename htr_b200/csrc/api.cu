@@ -203,7 +203,7 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
                           const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
-                          void* workspace, size_t workspace_bytes, htr_stream_t stream);
+                          void* workspace, size_t workspace_bytes, htr_stream_t stream, void* const* peer_y = nullptr, int npeer = 0);
 
 
 const char* htr_status_string(int status) {
@@ -446,12 +446,26 @@ int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride,
                         sv_table, count, workspace, workspace_bytes, stream);
 }
 
+int htr_linear_routed_peers(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count, int table_rows,
+                            const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
+                            const uint8_t* const* sv_table, int mt, int nt, int K, void* y, void* const* peer_y, int npeer, int prologue,
+                            void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+  if (count > 0 && (!x || !y || !route)) return HTR_ERR_NULL;
+  if (npeer < 1 || !peer_y) return HTR_ERR_BAD_SHAPE;
+  if (x_div < 1 || x_row_stride < 0 || table_rows < 1 || (prologue != HTR_PROLOGUE_NONE && prologue != HTR_PROLOGUE_SWIGLU))
+    return HTR_ERR_BAD_SHAPE;
+  if (prologue == HTR_PROLOGUE_SWIGLU && dtype != HTR_DTYPE_BF16) return HTR_ERR_BAD_DTYPE;
+  if (count > 0 && (!aligned16(x) || !aligned16(y))) return HTR_ERR_ALIGNMENT;
+  return launch_grouped(nullptr, nullptr, x, y, x_div, x_row_stride, route, table_rows, prologue, dtype, qweight_table, mt, nt, K, scales_table, su_table,
+                        sv_table, count, workspace, workspace_bytes, stream, peer_y, npeer);
+}
+
 // shared body of the grouped entry points: per-problem pointer lists (x_list / y_list), or a route into per-expert tables with the
 // activations and outputs as rows of two matrices
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
                           const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
-                          void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+                          void* workspace, size_t workspace_bytes, htr_stream_t stream, void* const* peer_y, int npeer) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (count < 0 || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
@@ -491,7 +505,10 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   p.slots = (int)split;
   p.independent = 0;
   p.cb = (float)codebook_scale();
-  p.npeer = 0;
+  if (npeer < 0 || npeer > 8 || (npeer > 0 && (!peer_y || !route))) return HTR_ERR_BAD_SHAPE;
+  for (int i = 0; i < npeer; ++i)
+    if (!peer_y[i] || !aligned16(peer_y[i])) return HTR_ERR_ALIGNMENT;
+  p.npeer = npeer;
   p.n_in = nt * 16;
   p.m_out = mt * 16;
   p.prologue = prologue;
@@ -506,7 +523,7 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   p.g_xrow_bytes = (long long)x_row_stride * esz;
   p.g_yrow_bytes = (long long)m * esz;
   p.peer_offset = 0;
-  for (int i = 0; i < 8; ++i) p.peer_y[i] = nullptr;
+  for (int i = 0; i < 8; ++i) p.peer_y[i] = i < npeer ? peer_y[i] : nullptr;
   for (int i = 0; i < 8; ++i) p.peer_flag[i] = nullptr;
   p.wblocks = 0;
   p.exact = 0;

@@ -109,8 +109,12 @@ struct GemvParams {
 __device__ __forceinline__ void signal_peers_when_last(const GemvParams& p, int* counters, int row_blocks) {
   __syncthreads();                                   // the stores of every warp are issued
   if (threadIdx.x == 0) {
-    __threadfence_system();                          // ... and ordered before the count (and the flags) for every GPU
+    // Release at GPU scope, then the count; the block that counts last acquires the others' stores with its own fence, which is
+    // system-wide and so also releases all of them to the peers ahead of the flags (fences are cumulative).  Only that one block
+    // pays for a system-wide fence.
+    __threadfence();
     if (atomicAdd(counters + kDoneCounter, 1) == row_blocks - 1) {
+      __threadfence_system();
       counters[kDoneCounter] = 0;
 #pragma unroll 1
       for (int pe = 0; pe < p.npeer; ++pe) atomicAdd_system(p.peer_flag[pe], 1u);
@@ -337,18 +341,24 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
   // everything above touched only the weights; what follows reads activations and writes shared state
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   bool predecessor_done = false;
+  bool ring_primed = false;                        // independent inputs: stages 1.. are issued behind the first activation loads
   if (!p.independent) {
+    // the activations come from the preceding kernel: while it drains, the whole ring is primed
+#pragma unroll
+    for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
+    ring_primed = true;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     predecessor_done = true;
   }
-  bool ring_primed = false;                        // stages 1.. are issued behind the first activation loads
   __shared__ float s_row_inv[MT];                  // RMSNorm scale per activation row (prologue 1)
   if (p.prologue == 1) {
     // RMSNorm fused into the activation staging: every CTA finds the row scale itself (the row is a few KB in L2), with the
     // copy ring fully primed first so that the weights keep streaming meanwhile
+    if (!ring_primed) {
 #pragma unroll
-    for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
-    ring_primed = true;
+      for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
+      ring_primed = true;
+    }
     __shared__ float s_ss[kGemvWarps];
 #pragma unroll
     for (int r = 0; r < MT; ++r) {
@@ -527,8 +537,11 @@ __global__ void __launch_bounds__(kGemvThreads, (MT == 1 ? 3 : MT == 2 ? 2 : 1))
         }
         if (row0 < p.m_out) store_quad(y_ptr, (size_t)r * p.m_out + row0, p.dtype, o);
       } else {
+        // (routed form: the problem's output row sits at the same byte offset in every peer's matrix as in y)
+        const size_t row_bytes = p.g_route ? (size_t)(static_cast<char*>(y_ptr) - static_cast<char*>(p.y)) : 0;
 #pragma unroll 1
-        for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);
+        for (int pe = 0; pe < p.npeer; ++pe)
+          store_quad(static_cast<char*>(p.peer_y[pe]) + row_bytes, (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, o);
       }
     }
     if (finish && p.npeer > 0 && p.peer_flag[0] != nullptr) signal_peers_when_last(p, p.counters, p.mt >> 3);

@@ -204,12 +204,16 @@ __global__ void __launch_bounds__(kGemvThreads, 3) packed_gemv_mma_kernel(const 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   bool predecessor_done = false;
   if (!p.independent) {
+    // the activations come from the preceding kernel: while it drains, the whole ring is primed
+#pragma unroll
+    for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     predecessor_done = true;
     if (p.prologue != 1 && first_item) x_first = load_item(first_r, first_hb);
-  }
+  } else {
 #pragma unroll
-  for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
+    for (int sgi = 1; sgi < kDepth; ++sgi) issue(sgi * kStageBytes);
+  }
   if (p.prologue == 1) {
     for (int r = 0; r < p.rows; ++r) {
       float ss = 0.f;

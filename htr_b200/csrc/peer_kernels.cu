@@ -57,13 +57,29 @@ __global__ void __launch_bounds__(256) moe_combine_peers_kernel(const void* __re
   if (peer_flag == nullptr) return;
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
+    __threadfence();                                   // release at GPU scope; the last block's system-wide fence carries all of it to the peers
     if (atomicAdd(done, 1) == (int)(gridDim.x * gridDim.y) - 1) {
+      __threadfence_system();
       *done = 0;
 #pragma unroll 1
       for (int pe = 0; pe < npeer; ++pe) atomicAdd_system(peer_flag[pe], 1u);
     }
   }
+}
+
+// out[t, :] = sum_j w[t, j] * dn[t * k + j, :], float32 sums in slot order, rounded once to the output type.  The same kernel closes the
+// layer on one GPU and on several (where dn holds the rows every rank delivered), so the two give the same bits.
+__global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const void* __restrict__ dn, int dtype, const float* __restrict__ w, int k, int h,
+                                                               void* __restrict__ out) {
+  const int t = blockIdx.y, col = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (col >= h) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j = 0; j < k; ++j) {
+    const float g = w[t * k + j];
+    const float4 v = htr::load_quad(dn, (size_t)(t * k + j) * h + col, dtype);
+    acc.x += g * v.x; acc.y += g * v.y; acc.z += g * v.z; acc.w += g * v.w;
+  }
+  htr::store_quad(out, (size_t)t * h + col, dtype, acc);
 }
 
 // out[t, :] = sum_r buf[r][t][:] in rank order (every rank adds identically), cast to the output type
@@ -100,6 +116,15 @@ int htr_moe_combine_peers(const void* dn, int dtype, const float* gates, int tok
   if (peer_flag && !done_counter) return HTR_ERR_NULL;
   moe_combine_peers_kernel<<<dim3((hidden + 1023) / 1024, tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       dn, dtype, gates, top_k, hidden, peer_out, npeer, (long long)slot_offset, peer_flag, done_counter);
+  return cudaGetLastError() == cudaSuccess ? HTR_OK : HTR_ERR_CUDA;
+}
+
+int htr_moe_weighted_sum(const void* dn, int dtype, const float* gates, int tokens, int top_k, int hidden, void* out, htr_stream_t stream) {
+  if (tokens <= 0) return HTR_OK;
+  if (!dn || !gates || !out) return HTR_ERR_NULL;
+  if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
+  if (top_k < 1 || hidden < 4 || hidden % 4 || tokens > 65535) return HTR_ERR_BAD_SHAPE;
+  moe_weighted_sum_kernel<<<dim3((hidden + 1023) / 1024, tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(dn, dtype, gates, top_k, hidden, out);
   return cudaGetLastError() == cudaSuccess ? HTR_OK : HTR_ERR_CUDA;
 }
 

@@ -254,11 +254,13 @@ def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K
     _lib.check(rc, "htr_linear_grouped")
 
 
-def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, out=None):
+def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, out=None, peer_ptrs=None):
     """One launch over `route.numel()` problems (htr_linear_routed): problem i multiplies activation row i // x_div of `x` by the
     packed matrix whose four tensor addresses sit in row route[i] of `tables` (four int64 CUDA tensors, one row per expert; a
     zero weight address, or a route entry outside the tables, skips the problem) and writes row i of the result [count, m].  With prologue=PROLOGUE_SWIGLU the rows of
-    x are [gate | up] of 2n bf16 values.  Nothing touches the host: the routing result stays on the device."""
+    x are [gate | up] of 2n bf16 values.  Nothing touches the host: the routing result stays on the device.
+    peer_ptrs (a list of device addresses: the [count, m] result matrix of every rank of an NVLink box as mapped into this process,
+    this rank's `out` among them) turns the launch into htr_linear_routed_peers: each row this rank computes is stored into all of them."""
     count = route.numel()
     dev = x.device
     if route.dtype != torch.int64 or not route.is_cuda or not x.is_contiguous() or x.dim() != 2:
@@ -270,10 +272,19 @@ def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, 
         raise _lib.HTRError("htr_linear_routed: unsupported sizes")
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
-        rc = _lib.lib.htr_linear_routed(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count, int(tables[0].numel()),
-                                        tables[0].data_ptr(),
-                                        tables[1].data_ptr(), tables[2].data_ptr(), tables[3].data_ptr(), mt, nt, K, out.data_ptr(), int(prologue),
-                                        ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream)
+        st = torch.cuda.current_stream(dev).cuda_stream
+        if peer_ptrs is None:
+            rc = _lib.lib.htr_linear_routed(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count, int(tables[0].numel()),
+                                            tables[0].data_ptr(), tables[1].data_ptr(), tables[2].data_ptr(), tables[3].data_ptr(), mt, nt, K,
+                                            out.data_ptr(), int(prologue), ws.data_ptr(), ws.numel(), st)
+        else:
+            import ctypes
+
+            host = (ctypes.c_void_p * len(peer_ptrs))(*[int(v) for v in peer_ptrs])
+            rc = _lib.lib.htr_linear_routed_peers(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count,
+                                                  int(tables[0].numel()), tables[0].data_ptr(), tables[1].data_ptr(), tables[2].data_ptr(),
+                                                  tables[3].data_ptr(), mt, nt, K, out.data_ptr(), host, len(host), int(prologue),
+                                                  ws.data_ptr(), ws.numel(), st)
         _lib.check(rc, "htr_linear_routed")
     return out
 

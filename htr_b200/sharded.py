@@ -98,7 +98,8 @@ class PeerGather:
     raises this rank's word in every rank's flag array), with `wait()`, a bounded wait on the current stream.
 
     Two alternating buffers: a rank that is one call ahead writes the half that its peers have finished reading (a rank consumes
-    the result of call i - 1, on its stream, before it launches call i + 1)."""
+    the result of call i - 1, on its stream, before it launches call i + 1).  A CUDA graph that is replayed back to back must
+    therefore capture an even number of calls (both halves), or end with a barrier of its own."""
 
     def __init__(self, world, rank, max_rows, rows_per_rank, dtype, device, group=None):
         import os
@@ -241,6 +242,7 @@ class ExpertParallelMoE:
         self.linear_fn = linear_fn or _default_linear()
         self._tables = None
         self._peer = None
+        self._rows = {}
 
     def _address_tables(self, dev):
         """int64 device tensors [all experts] with the addresses of each expert's wire tensors (for the grouped kernel);
@@ -252,12 +254,39 @@ class ExpertParallelMoE:
             self._tables = {w: tuple(col(w, i) for i in range(4)) for w in ("gate_up", "down")}
         return self._tables
 
-    def routed_outputs(self, x, topk_ids):
-        """Expert outputs of every (token, slot) pair owned by this rank, [T * k, h] in x.dtype, with two routed launches over all
-        pairs: gate_up reads token row pair // k, down reads the pair's [gate | up] row and applies SwiGLU while staging it (bf16;
-        other dtypes use a separate activation step).  Routing stays on the device (no host round trip, capturable in a CUDA
-        graph); pairs routed to another rank's experts are skipped by the kernel (null weight address) and stay zero."""
-        from . import ops
+    def _row_exchange(self, pairs, hdim, dtype, dev):
+        """Symmetric-memory matrices [2 halves][pairs][h] that every rank maps: a routed launch stores the output row of each pair
+        this rank owns into all of them.  Two halves alternate (a rank one call ahead writes the half its peers have finished
+        reading: it passed the barrier of the call before, which its peers reach only after they have consumed the call before that;
+        a CUDA graph replayed back to back must capture an even number of calls)."""
+        key = (dtype, hdim)
+        ex = self._rows.get(key)
+        if ex is None or ex["pairs"] < pairs:
+            import os
+
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
+            import torch.distributed._symmetric_memory as symm_mem
+
+            grp = self.group if self.group is not None else dist.group.WORLD
+            cap = max(512, pairs)
+            buf = symm_mem.empty((2, cap, hdim), dtype=dtype, device=dev)
+            hdl = symm_mem.rendezvous(buf, grp)
+            half_bytes = cap * hdim * buf.element_size()
+            ptrs = [[int(p) + hf * half_bytes for p in hdl.buffer_ptrs] for hf in (0, 1)]
+            ex = dict(pairs=cap, buf=buf, hdl=hdl, ptrs=ptrs, flip=0)
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=grp)
+            self._rows[key] = ex
+        return ex
+
+    def routed_outputs(self, x, topk_ids, exchange=False):
+        """Expert outputs of every (token, slot) pair, [T * k, h] in x.dtype, with two routed launches over all pairs: gate_up reads
+        token row pair // k, down reads the pair's [gate | up] row and applies SwiGLU while staging it (bf16; other dtypes use a
+        separate activation step).  Routing stays on the device (no host round trip, capturable in a CUDA graph); pairs routed to
+        another rank's experts are skipped by the kernel (null weight address).  Without `exchange` their rows stay zero; with it
+        the down launch stores each row into every rank's matrix (htr_linear_routed_peers) and, after one barrier across the ranks,
+        every rank holds the rows of all pairs, each computed by the rank that owns its expert."""
+        from . import _lib, ops
 
         T, hdim = x.shape
         k = topk_ids.shape[1]
@@ -269,17 +298,39 @@ class ExpertParallelMoE:
         mt_dn, nt_dn, _ = any_e["down"][0].shape
         K = W // 8
         x = x.contiguous()
-        skip = self.world > 1                                            # rows of skipped pairs must read as zero
+        skip = self.world > 1 and not exchange                          # rows of skipped pairs must read as zero
         alloc = torch.zeros if skip else torch.empty
+        # (with `exchange`, the gate_up rows of pairs owned elsewhere are never read: the down launch skips the same pairs)
         gu = ops.linear_routed(x, route, tabs["gate_up"], mt_gu, nt_gu, K, x_div=k, out=alloc(T * k, mt_gu * 16, dtype=x.dtype, device=dev))
-        dn = alloc(T * k, mt_dn * 16, dtype=x.dtype, device=dev)
         if x.dtype == torch.bfloat16:
-            ops.linear_routed(gu, route, tabs["down"], mt_dn, nt_dn, K, prologue=ops.PROLOGUE_SWIGLU, out=dn)
+            act, prologue = gu, ops.PROLOGUE_SWIGLU
         else:
             inter = mt_gu * 8
-            act = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).contiguous()
-            ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, out=dn)
+            act, prologue = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).contiguous(), ops.PROLOGUE_NONE
+        if not exchange:
+            return ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=alloc(T * k, mt_dn * 16, dtype=x.dtype, device=dev))
+        ex = self._row_exchange(T * k, mt_dn * 16, x.dtype, dev)
+        half = ex["flip"]
+        ex["flip"] ^= 1
+        dn = ex["buf"][half, :T * k]
+        ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=dn, peer_ptrs=ex["ptrs"][half])
+        ex["hdl"].barrier(channel=0)
         return dn
+
+    @staticmethod
+    def weighted_sum(dn, topk_w, T, k):
+        """y[t] = sum_j w[t, j] * dn[t * k + j] (htr_moe_weighted_sum: float32 sums in slot order, one rounding)."""
+        from . import _lib
+
+        dev = dn.device
+        gates = topk_w.to(device=dev, dtype=torch.float32).contiguous()
+        out = torch.empty(T, dn.shape[1], dtype=dn.dtype, device=dev)
+        code = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}[dn.dtype]
+        with torch.cuda.device(dev):
+            rc = _lib.lib.htr_moe_weighted_sum(dn.data_ptr(), code, gates.data_ptr(), T, k, dn.shape[1], out.data_ptr(),
+                                               torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(rc, "htr_moe_weighted_sum")
+        return out
 
     def partial_grouped(self, x, topk_ids, topk_w):
         """Contribution of this rank's experts, float32 [T, h]: the routed launches + the gate-weighted sum over the slots."""
@@ -359,14 +410,22 @@ class ExpertParallelMoE:
         return out
 
     def __call__(self, x, topk_ids, topk_w, grouped=None, combine=None):
-        """combine: "peer" = peer stores + delivery flags + rank-ordered add (CUDA, grouped form, up to 64 tokens),
-        "nccl" = all-gather of the float32 parts + rank-ordered add; default: "peer" where it applies."""
+        """combine (several ranks, CUDA, grouped form, NCCL group; default "rows" where it applies):
+        "rows" = the down launch stores each pair's row into every rank, one barrier, then the same weighted sum as on one GPU
+                 (the result equals the single-GPU one bit for bit; up to 4096 pairs);
+        "peer" = peer stores of the ranks' float32 partial sums + rank-ordered add (up to 64 tokens);
+        "nccl" = all-gather of the float32 parts + rank-ordered add."""
         use_grouped = (x.is_cuda and self.count > 0) if grouped is None else grouped
         T, hdim = x.shape
-        if (self.world > 1 and use_grouped and x.is_cuda and T <= 64 and combine in (None, "peer") and self.num_experts >= self.world
-                and dist.get_backend(self.group) == "nccl"):
+        k = topk_ids.shape[1]
+        if self.world == 1 and use_grouped and x.is_cuda:
+            return self.weighted_sum(self.routed_outputs(x, topk_ids), topk_w, T, k)
+        peers_ok = (self.world > 1 and use_grouped and x.is_cuda and self.num_experts >= self.world and dist.get_backend(self.group) == "nccl")
+        if peers_ok and combine in (None, "rows") and T * k <= 4096:
+            return self.weighted_sum(self.routed_outputs(x, topk_ids, exchange=True), topk_w, T, k)
+        if peers_ok and combine in (None, "peer") and T <= 64:
             dn = self.routed_outputs(x, topk_ids)
-            return self._peer_combine(dn, topk_w, T, topk_ids.shape[1], hdim, x.dtype)
+            return self._peer_combine(dn, topk_w, T, k, hdim, x.dtype)
         part = self.partial_grouped(x, topk_ids, topk_w) if use_grouped else self.partial(x, topk_ids, topk_w)
         if self.world == 1:
             return part.to(x.dtype)

@@ -121,6 +121,9 @@ int htr_peer_wait(const unsigned* flags, unsigned* epoch, int nranks, int count,
 int htr_moe_combine_peers(const void* dn, int dtype, const float* gates, int tokens, int top_k, int hidden, float* const* peer_out,
                           int npeer, int64_t slot_offset, unsigned* const* peer_flag /* may be NULL */, int* done_counter,
                           htr_stream_t stream);
+/* Closing step of a mixture-of-experts layer: out[t, :] = sum_j gates[t, j] * dn[t * top_k + j, :], float32 sums in slot order, rounded
+ * once to `dtype` (dn and out share it).  The same call closes the layer on one GPU and, after htr_linear_routed_peers and a barrier, on several: equal bits.  (The reference leaves the combine to the serving framework.) */
+int htr_moe_weighted_sum(const void* dn, int dtype, const float* gates, int tokens, int top_k, int hidden, void* out, htr_stream_t stream);
 int htr_rank_sum(const float* buf, int world, int64_t rank_stride, int tokens, int hidden, void* out, int dtype, htr_stream_t stream);
 
 /* Grouped form of htr_linear: `count` packed linears of one shape [m, n] and width K, one activation row each, in ONE launch
@@ -162,6 +165,16 @@ int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride,
                       const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
                       const uint8_t* const* sv_table, int mt, int nt, int K, void* y, int prologue, void* workspace,
                       size_t workspace_bytes, htr_stream_t stream);
+
+/* htr_linear_routed for expert parallelism on one NVLink box: the output row of every problem this rank owns (non-NULL weight entry)
+ * is stored, with plain peer stores, into the matrix of each peer at the byte offset it has in y (peer_y[i]: the peers' [count][m]
+ * matrices as mapped into this process, this rank's own among them; y itself is only the base the offsets are taken from and is not
+ * written).  After the ranks have ordered themselves (a barrier across them) every rank holds the rows of all problems, each
+ * computed by the rank that owns its expert, and combines them exactly as a single GPU would.  (No counterpart in the reference.) */
+int htr_linear_routed_peers(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count, int table_rows,
+                            const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
+                            const uint8_t* const* sv_table, int mt, int nt, int K, void* y, void* const* peer_y, int npeer, int prologue,
+                            void* workspace, size_t workspace_bytes, htr_stream_t stream);
 
 /* Padded form (the reference's HTRHCLinearMethod.apply, htr/vllm_plugin.py:313-326: F.pad of the input to n_pad, slice of
  * the output to m_out, both as separate copies there): the stored tensors cover a padded [m = 16*mt, n = 16*nt] matrix, x has

@@ -196,13 +196,24 @@ def _nccl_worker(rank, world, port, q):
         y_loop = moe(xm.to(dev), ids, w, grouped=False).float().cpu()
         want = _moe_reference(experts, xm, ids, w, _oracle_linear())
         ok = ok and float((y_grp - want).norm() / want.norm()) <= 1e-5 and float((y_loop - want).norm() / want.norm()) <= 1e-5
-        # the combine by peer stores and delivery flags (the default above) against the all-gather form, and twice more in a row
-        # (the two halves of the buffers alternate)
+        # the default combine across ranks ("rows": the down launch stores each pair's row into every rank, one barrier, the same
+        # weighted sum as on one GPU) equals a one-rank layer that holds all experts, bit for bit; three calls in a row (the two
+        # halves of the exchange matrix alternate), float32 and bf16
+        solo = None
+        for r in range(world):                                               # every rank creates every group, as torch.distributed requires
+            g = dist.new_group([r])
+            solo = g if r == rank else solo
+        one = ExpertParallelMoE(experts, device=dev, group=solo)
+        for xin in (xm, xm.bfloat16(), xm * 2):
+            ok = ok and bool(torch.equal(moe(xin.to(dev), ids, w), one(xin.to(dev), ids, w)))
+        # the other two combines (float32 partial sums by peer stores, or by all-gather; rank-ordered add) agree to rounding
         y_nccl = moe(xm.to(dev), ids, w, combine="nccl").float().cpu()
         ok = ok and float((y_grp - y_nccl).norm() / y_nccl.norm()) <= 1e-6
+        y_peer = moe(xm.to(dev), ids, w, combine="peer").float().cpu()
+        ok = ok and float((y_peer - y_nccl).norm() / y_nccl.norm()) <= 1e-6
         for order in ("barrier", "flags", "barrier"):
             sharded_mod.PEER_ORDER = order
-            ok = ok and bool(torch.equal(moe(xm.to(dev), ids, w).float().cpu(), y_grp))
+            ok = ok and bool(torch.equal(moe(xm.to(dev), ids, w, combine="peer").float().cpu(), y_peer))
         sharded_mod.PEER_ORDER = "barrier"
         ok = ok and int(moe._peer["status"].item()) == 0
         torch.cuda.synchronize()
