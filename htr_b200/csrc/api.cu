@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "packed_gemv_mma.cuh"
+#include "packed_gemv_tm.cuh"
 
 namespace htr {
 int run_decode_raw(int K, const uint32_t* qw, int16_t* out, long long ntiles, cudaStream_t st);
@@ -60,13 +61,25 @@ static int gemv_mma_config(int K, int rows, int* ctas, int* cap) {
   return (int)cudaErrorInvalidValue;
 }
 
-// Which kernel serves single problems of up to four activation rows: 0 = CUDA-core GEMV, 1 = warp-MMA GEMV, -1 = by measurement
-// (gemv_kind below).  HTR_GEMV_KERNEL in the environment sets the default of the process.
+static int gemv_tm_config(int K, int rows, int* ctas, int* cap) {
+  switch (K) {
+    case 2: return packed_gemv_tm_config<2>(rows, ctas, cap);
+    case 3: return packed_gemv_tm_config<3>(rows, ctas, cap);
+    case 4: return packed_gemv_tm_config<4>(rows, ctas, cap);
+    case 5: return packed_gemv_tm_config<5>(rows, ctas, cap);
+    case 6: return packed_gemv_tm_config<6>(rows, ctas, cap);
+    case 8: return packed_gemv_tm_config<8>(rows, ctas, cap);
+  }
+  return (int)cudaErrorInvalidValue;
+}
+
+// Which kernel serves single problems of up to four activation rows: 0 = CUDA-core GEMV, 1 = warp-MMA GEMV, 2 = tensor-memory
+// GEMV, -1 = by measurement (gemv_kind below).  HTR_GEMV_KERNEL in the environment sets the default of the process.
 static int gemv_kind_default() {
   static const int kind = [] {
     const char* v = std::getenv("HTR_GEMV_KERNEL");
     const int k = v ? std::atoi(v) : -1;
-    return k < -1 || k > 1 ? -1 : k;
+    return k < -1 || k > 2 ? -1 : k;
   }();
   return kind;
 }
@@ -125,15 +138,38 @@ static int cached_mma_config(int dev, int K, int rows, int* ctas, int* cap) {
   return 0;
 }
 
+// tensor-memory kernel: CTAs per SM and the window cap, per (device, K, rows)
+static int cached_tm_config(int dev, int K, int rows, int* ctas, int* cap) {
+  struct Entry { int ctas, cap; };
+  static Entry cache[64][9][kTmRows + 1] = {};
+  static std::mutex mu;
+  if (dev < 0 || dev >= 64) return gemv_tm_config(K, rows, ctas, cap);
+  std::lock_guard<std::mutex> lock(mu);
+  Entry& slot = cache[dev][K][rows];
+  if (slot.ctas == 0) {
+    int c = 0, w = 0;
+    if (const int e = gemv_tm_config(K, rows, &c, &w)) return e;
+    slot.ctas = c;
+    slot.cap = w;
+  }
+  *ctas = slot.ctas;
+  *cap = slot.cap;
+  return 0;
+}
+
+// the tensor-memory kernel serves up to four rows of plain activations, rows of at most 16384 columns (32-bit accumulators)
+static bool tm_serves(int M, int n, int prologue) { return M >= 1 && M <= kTmRows && n <= kTmMaxCols && prologue == 0; }
+
 static int g_kind_override = -1;                       // -1: environment default, else the kind
 // Measured policy (4096x12288 K4, bf16): one row is cheapest on the CUDA-core kernel -- an int8 mma.sync costs about as many issue
 // slots as the byte sums and multiply-adds it replaces, and its activation staging is heavier; from two rows on the MMA serves the
 // extra rows for free.  Three or four float32 / fp16 rows (which would need more planes than an MMA holds) and five to eight rows
 // stay on the CUDA-core kernel.
-static int gemv_kind(int M, int dtype = HTR_DTYPE_BF16) {
-  if (!mma_serves(M, dtype)) return 0;
+static int gemv_kind(int M, int dtype = HTR_DTYPE_BF16, int n = 0, int prologue = 0) {
   const int kind = g_kind_override >= 0 ? g_kind_override : gemv_kind_default();
-  return kind >= 0 ? kind : (M >= 2 ? 1 : 0);
+  if (kind == 2 && n > 0 && tm_serves(M, n, prologue)) return 2;
+  if (!mma_serves(M, dtype)) return 0;
+  return kind == 0 || kind == 1 ? kind : (M >= 2 ? 1 : 0);
 }
 
 static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
@@ -145,6 +181,26 @@ static int make_plan(int M, int m, int n, int K, Plan* out, int kind = 0) {
   Plan pl;
   pl.rows_t = template_rows(M);
   int per_sm = 0, window_cap = 0;
+  if (kind == 2) {
+    // flat ranges of 64-column units over two thread blocks per SM; a run of L units touches at most L/2 + 1 blocks
+    if (const int ce = cached_tm_config(dev, K, M, &per_sm, &window_cap)) return cuda_fail(ce);
+    pl.rbs = m / 128;
+    if (pl.rbs >= kTmFaultWord) return HTR_ERR_TOO_LARGE;
+    pl.cg = n / 64;
+    pl.units = pl.rbs * pl.cg;
+    const long long slots_all = (long long)sms * per_sm;
+    pl.split = 0;
+    pl.grid = (int)(slots_all < pl.units ? slots_all : pl.units);
+    const int per_cta = pl.units / pl.grid;
+    pl.slots = (pl.cg + per_cta - 1) / per_cta + 1;
+    const int longest = per_cta + 1 < pl.cg ? per_cta + 1 : pl.cg;
+    int need = longest / 2 + 1;
+    if (need > pl.cg / 2) need = pl.cg / 2;
+    const int windows = (need + window_cap - 1) / window_cap;
+    pl.wblocks = (need + windows - 1) / windows;
+    *out = pl;
+    return HTR_OK;
+  }
   if (kind == 1) {
     if (const int ce = cached_mma_config(dev, K, M, &per_sm, &window_cap)) return cuda_fail(ce);
   } else {
@@ -224,7 +280,9 @@ const char* htr_status_string(int status) {
 int htr_last_cuda_error(void) { return t_last_cuda; }
 int htr_version(void) { return 100; }
 
-void htr_set_gemv_kernel(int kind) { g_kind_override = kind < 0 || kind > 1 ? -1 : kind; }   // -1: back to the default
+void htr_set_gemv_kernel(int kind) { g_kind_override = kind < 0 || kind > 2 ? -1 : kind; }   // -1: back to the default
+
+size_t htr_linear_fault_offset(void) { return (size_t)kTmFaultWord * 4; }
 
 int htr_decode_raw(const void* qweight, int64_t ntiles, int K, int16_t* out, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
@@ -253,20 +311,25 @@ size_t htr_linear_workspace_bytes(int M, int m, int n, int K) {
   Plan pl;
   if (make_plan(M, m, n, K, &pl) != HTR_OK) return 0;
   size_t slots = (size_t)pl.slots;
-  if (M <= kMmaRows) {                                   // either kernel may serve the call: size for both
+  if (M <= kMmaRows) {                                   // any of the kernels may serve the call: size for all
     Plan mma;
     if (make_plan(M, m, n, K, &mma, 1) != HTR_OK) return 0;
     if ((size_t)mma.slots > slots) slots = (size_t)mma.slots;
+    if (tm_serves(M, n, 0)) {
+      Plan tm;
+      if (make_plan(M, m, n, K, &tm, 2) != HTR_OK) return 0;
+      if ((size_t)tm.slots > slots) slots = (size_t)tm.slots;
+    }
   }
-  // up to two rows may be asked for in the integer-exact form, whose partial sums are 64-bit
-  return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * (M <= 2 ? sizeof(long long) : sizeof(float));
+  // up to four rows may run in an integer-exact form, whose partial sums are 64-bit
+  return counter_bytes(m) + (size_t)pl.rbs * slots * pl.rows_t * 128 * (M <= kMmaRows ? sizeof(long long) : sizeof(float));
 }
 
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (M < 1 || M > HTR_GEMV_MAX_ROWS || m <= 0 || n <= 0 || m % 128 || n % 128) return HTR_ERR_BAD_SHAPE;
   Plan pl;
-  const int rc = make_plan(M, m, n, K, &pl, gemv_kind(M));
+  const int rc = make_plan(M, m, n, K, &pl, gemv_kind(M, HTR_DTYPE_BF16, n, 0));
   if (rc != HTR_OK) return rc;
   if (grid) *grid = pl.grid;
   if (slots_per_block) *slots_per_block = pl.slots;
@@ -343,11 +406,14 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   const int m = mt * 16, n = nt * 16;
   Plan pl;
   // the integer-exact form: up to two rows (four byte planes per activation), plain activations
-  const bool exact = (flags & HTR_LINEAR_EXACT_SUMS) && M <= 2 && prologue == 0;
-  const int kind = exact ? 1 : gemv_kind(M, dtype);
+  // (the tensor-memory kernel always sums in integers; its grid of integers differs from the warp-MMA kernel's, so a process
+  // should keep to one of them where results of differently sharded launches are compared bit for bit)
+  int kind = gemv_kind(M, dtype, n, prologue);
+  const bool exact = (flags & HTR_LINEAR_EXACT_SUMS) && prologue == 0 && (M <= 2 || kind == 2);
+  if (exact && kind != 2) kind = 1;
   const int rc = make_plan(M, m, n, K, &pl, kind);
   if (rc != HTR_OK) return rc;
-  const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * (exact ? sizeof(long long) : sizeof(float));
+  const size_t need = counter_bytes(m) + (size_t)pl.rbs * pl.slots * pl.rows_t * 128 * ((exact || kind == 2) ? sizeof(long long) : sizeof(float));
   if (!workspace || workspace_bytes < need) return HTR_ERR_WORKSPACE;
 
   GemvParams p;
@@ -395,6 +461,17 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
   p.cb = (float)codebook_scale();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int e = 0;
+  if (kind == 2) {
+    switch (K) {
+      case 2: e = launch_packed_gemv_tm<2>(p, pl.grid, st); break;
+      case 3: e = launch_packed_gemv_tm<3>(p, pl.grid, st); break;
+      case 4: e = launch_packed_gemv_tm<4>(p, pl.grid, st); break;
+      case 5: e = launch_packed_gemv_tm<5>(p, pl.grid, st); break;
+      case 6: e = launch_packed_gemv_tm<6>(p, pl.grid, st); break;
+      case 8: e = launch_packed_gemv_tm<8>(p, pl.grid, st); break;
+    }
+    return e ? cuda_fail(e) : HTR_OK;
+  }
   if (kind == 1) {
     switch (K) {
       case 2: e = launch_packed_gemv_mma<2>(p, pl.grid, st); break;

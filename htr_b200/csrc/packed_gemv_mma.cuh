@@ -238,7 +238,8 @@ __global__ void __launch_bounds__(kGemvThreads, 3) packed_gemv_mma_kernel(const 
 
   // Exact form (p.exact): one power-of-two scale per activation row for the whole launch, so that every window's integers lie
   // on one grid and all sums -- across windows, across thread blocks -- stay in 64-bit integers.  The scale comes from a bound
-  // that needs no transform: |xt_j| <= sqrt(128) max_i |x_i| < 2^4.5 max|x|.  Every CTA scans the row (a few KB from L2).
+  // that needs no transform: |v_j| <= 128 max_i |x_i| for the unnormalised transform v that is quantised below (met when su * x
+  // is a row of the Hadamard matrix).  Every CTA scans the row (a few KB from L2).
   const bool exact = p.exact != 0;
   if (exact) {
     for (int r = 0; r < p.rows; ++r) {
@@ -254,8 +255,8 @@ __global__ void __launch_bounds__(kGemvThreads, 3) packed_gemv_mma_kernel(const 
       if (tid == 0) {
         unsigned all = 0u;
         for (int k = 0; k < kGemvWarps; ++k) all = max(all, __float_as_uint(s_ss[k]));
-        // four binades up covers the factor sqrt(128) (and the part of a binade above the leading bit)
-        s_rowmax[r] = all >= 0x7F800000u ? 0x7FC00000u : min(all + (4u << 23), 0x7F000000u);
+        // seven binades up: the factor 128
+        s_rowmax[r] = all >= 0x7F800000u ? 0x7FC00000u : min(all + (7u << 23), 0x7F000000u);
       }
       __syncthreads();
     }

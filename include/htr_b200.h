@@ -254,10 +254,15 @@ int htr_viterbi_last_cuda_error(void);
 int htr_codebook_f32(float* out, htr_stream_t stream);
 
 /* Which kernel serves htr_linear and its variants for up to four activation rows: 0 = the CUDA-core GEMV, 1 = the warp-MMA GEMV
- * (hash words as int8 mma.sync fragments; one or two rows of any type, three or four bf16 rows), -1 = the default: environment
- * variable HTR_GEMV_KERNEL if set, else the warp-MMA GEMV wherever it applies.  Grouped launches and five to eight rows always
- * run on the CUDA-core GEMV.  (Measurement and test knob; no counterpart in the reference.) */
+ * (hash words as int8 mma.sync fragments; one or two rows of any type, three or four bf16 rows), 2 = the tensor-memory GEMV
+ * (hash words as the A operand of tcgen05.mma.kind::i8 in tensor memory; up to four rows of any type, plain activations, rows of
+ * at most 16384 columns; integer-exact sums always), -1 = the default: environment variable HTR_GEMV_KERNEL if set, else the
+ * measured policy.  A kind that does not serve a call falls back to the default policy for that call.  Grouped launches and five
+ * to eight rows always run on the CUDA-core GEMV.  (Measurement and test knob; no counterpart in the reference.) */
 void htr_set_gemv_kernel(int kind);
+/* Byte offset, inside the workspace of htr_linear and its variants, of a 32-bit word that the tensor-memory GEMV sets to 1 when
+ * one of its bounded waits ran out (the launch then left rows of y unwritten).  Zero in a healthy run; the caller clears it. */
+size_t htr_linear_fault_offset(void);
 /* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block);
 

@@ -204,3 +204,18 @@ def test_exact_sums_do_not_depend_on_the_launch_decomposition(coracle, dev, K, m
     ref = coracle.linear(x.numpy(), qw.numpy(), sc.numpy(), su.numpy(), sv.numpy())
     assert rel(y.cpu().numpy(), ref) <= 1e-5
     check_bf16(yb, coracle.linear(x.bfloat16().float().numpy(), qw.numpy(), sc.numpy(), su.numpy(), sv.numpy()))
+
+
+def test_exact_sums_hold_at_the_bound_of_the_row_scale(coracle, dev):
+    """The exact form scales a row by a bound on its transform, 128 max|x|.  An input that meets it (su * x constant: the first
+    output of every 128-column block is 128 times that constant) must not overflow the integer grid."""
+    from htr_b200 import ops, wire
+
+    m, n, K = 256, 2048, 4
+    qw, sc, su, sv = wire.random_packed(m, n, K, seed=5)
+    signs = 1.0 - 2.0 * torch.from_numpy(np.unpackbits(su.numpy(), bitorder="little").astype(np.float32))
+    x = (1.75 * signs).reshape(1, n)
+    ref = coracle.linear(x.numpy(), qw.numpy(), sc.numpy(), su.numpy(), sv.numpy())
+    with ops.exact_sums():
+        y = ops.linear(x.to(dev), *[t.to(dev) for t in (qw, sc, su, sv)]).cpu().numpy()
+    assert rel(y, ref) <= 1e-5
