@@ -322,6 +322,36 @@ def batch_sweep_record(torch, dev, weights_by_k, reps):
     return out
 
 
+def gemv_kernels_record(torch, dev, weights_by_k, reps):
+    """The three GEMV kernels side by side at batch 1 on the 4096x12288 linears of the main workload (resident copies, more than
+    L2 per width): CUDA cores (the default at one row), warp-level int8 MMA, tcgen05 with the hashes in tensor memory.
+    Independent launches (consecutive launches overlap), one CUDA graph per kernel and width."""
+    from htr_b200 import _lib, ops
+
+    names = {0: "packed_gemv_kernel<K,1> (CUDA cores)", 1: "packed_gemv_mma_kernel<K,4> (mma.sync u8 x s8)",
+             2: "packed_gemv_tm_kernel<K> (tcgen05.mma kind::i8, A operand in tensor memory)"}
+    out = {"shape_m_x_n": [4096, 12288], "batch": 1, "launch_form": "independent inputs", "kernels": names}
+    try:
+        for K, ws in weights_by_k.items():
+            n = ws[0][0].shape[1] * 16
+            nbytes = payload_bytes(ws[0][0].shape[0] * 16, n, K)
+            x = torch.randn(1, n, device=dev, generator=torch.Generator(device=dev).manual_seed(K)).bfloat16()
+            row = {}
+            for kind in (0, 1, 2):
+                _lib.lib.htr_set_gemv_kernel(kind)
+
+                def run():
+                    with ops.independent_inputs():
+                        for w in ws:
+                            ops.linear(x, *w)
+                ms = _time_graph(torch, None, 1, dev, run, reps) / len(ws)
+                row[f"kind{kind}"] = {"us": round(1e3 * ms, 2), "packed_GBps": round(nbytes / (ms * 1e-3) / 1e9, 1)}
+            out[f"K{K}"] = row
+    finally:
+        _lib.lib.htr_set_gemv_kernel(-1)
+    return out
+
+
 def decoder_record(torch, dist, rank, world, dev):
     """Benchmark configuration 2: the dense 9B-class decoder (36 layers, K4 trunk and head), 16-token prompt, 256 greedy tokens,
     batch 1, one CUDA graph per decode step.  Several ranks = that many replicas (the trunk does not shard)."""
@@ -604,6 +634,7 @@ def run_ours(args):
         if world == 1:
             by_k = {K: [it["w"] for it in items if it["m"] == 4096] for K, items in zip(WIDTHS, groups)}
             extras["batch_sweep"] = batch_sweep_record(torch, dev, by_k, max(3, args.steps // 2))
+            extras["gemv_kernels"] = gemv_kernels_record(torch, dev, by_k, max(3, args.steps // 2))
             del by_k
         # free the headline workload before the larger models are built
         groups.clear()

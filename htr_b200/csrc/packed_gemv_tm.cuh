@@ -68,7 +68,7 @@ __device__ __forceinline__ void tm_mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // bounded wait for the phase with the given parity; false when the limit ran out or another role has already failed
-__device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity, const volatile int* fail) {
+__device__ __forceinline__ bool tm_mbar_wait_slow(uint32_t bar, uint32_t parity, const volatile int* fail) {
   for (unsigned it = 0; it < kTmSpin; ++it) {
     uint32_t done;
     asm volatile(
@@ -80,6 +80,15 @@ __device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity, cons
     if ((it & 255u) == 255u && *fail) return false;
   }
   return false;
+}
+__device__ __forceinline__ bool tm_mbar_wait(uint32_t bar, uint32_t parity, const volatile int* fail) {
+  uint32_t done;                                       // the common case: the phase is already complete
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+               : "=r"(done)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  if (done) return true;
+  return tm_mbar_wait_slow(bar, parity, fail);
 }
 __device__ __forceinline__ uint64_t tm_desc_b(uint32_t smem_addr) {
   // start address, LBO, SBO in 16-byte units; descriptor version 1 (sm_100); layout type 0 = no swizzle
@@ -281,10 +290,17 @@ __global__ void __launch_bounds__(kTmThreads, 2) packed_gemv_tm_kernel(const Gem
   // |v_j| <= 128 max_i |x_i| for the unnormalised transform v.  Every CTA scans the rows (a few KB from L2).
   for (int r = 0; r < p.rows; ++r) {
     unsigned mx = 0u;
-    for (int e = tid; e < (n >> 2); e += kTmThreads) {
-      const float4 v = load_x(p.x, r, 4 * e, p.n_in, p.dtype);
-      mx = max(max(mx, __float_as_uint(v.x) & 0x7FFFFFFFu), max(__float_as_uint(v.y) & 0x7FFFFFFFu,
-               max(__float_as_uint(v.z) & 0x7FFFFFFFu, __float_as_uint(v.w) & 0x7FFFFFFFu)));   // NaN and Inf patterns compare largest
+    for (int e0 = tid; e0 < (n >> 2); e0 += 4 * kTmThreads) {       // four loads in flight per thread
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = e0 + j * kTmThreads;
+        v[j] = e < (n >> 2) ? load_x(p.x, r, 4 * e, p.n_in, p.dtype) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        mx = max(max(mx, __float_as_uint(v[j].x) & 0x7FFFFFFFu), max(__float_as_uint(v[j].y) & 0x7FFFFFFFu,
+                 max(__float_as_uint(v[j].z) & 0x7FFFFFFFu, __float_as_uint(v[j].w) & 0x7FFFFFFFu)));   // NaN and Inf patterns compare largest
     }
     mx = __reduce_max_sync(kFullWarp, mx);
     if (lane == 0) s_red[warp] = __uint_as_float(mx);

@@ -55,11 +55,8 @@ int packed_gemv_tm_config<HTR_INST_K>(int rows, int* ctas_per_sm, int* window_ca
   int cap = budget / tm_window_bytes(1);
   if (cap > row_cap) cap = row_cap;
   if (cap < 1) return (int)cudaErrorLaunchOutOfResources;
-  int ctas = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas, packed_gemv_tm_kernel<HTR_INST_K>, kTmThreads,
-                                                    TmRing<HTR_INST_K>::bytes + tm_window_bytes(cap));
-  if (e != cudaSuccess) return (int)e;
-  if (ctas < 1) return (int)cudaErrorLaunchOutOfResources;
+  // (two thread blocks fit by the arithmetic above; tensor memory, 256 columns each, allows no more)
+  const int ctas = 2;
   *ctas_per_sm = ctas < 2 ? ctas : 2;
   *window_cap = cap;
   return 0;
