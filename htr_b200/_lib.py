@@ -68,7 +68,7 @@ def _load():
     lib.htr_dec_rope_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
     lib.htr_linear_plan.argtypes = [i32, i32, i32, i32, ctypes.POINTER(i32), ctypes.POINTER(i32)]
     lib.htr_linear_peers_signal.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, i64, vp, sz, vp, ctypes.c_uint]
-    lib.htr_linear_routed_peers.argtypes = [vp, i32, i32, i64, vp, i32, i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, i32, vp, sz, vp]
+    lib.htr_linear_routed_peers.argtypes = [vp, i32, i32, i64, vp, i32, i32, vp, vp, vp, vp, i32, i32, i32, vp, vp, i32, i32, i32, vp, sz, vp]
     lib.htr_peer_wait.argtypes = [vp, vp, i32, i32, vp, vp]
     lib.htr_moe_combine_peers.argtypes = [vp, i32, vp, i32, i32, i32, vp, i32, i64, vp, vp, vp]
     lib.htr_moe_weighted_sum.argtypes = [vp, i32, vp, i32, i32, i32, vp, vp]

@@ -259,7 +259,8 @@ static int launch_linear(const void* x, int dtype, int M, int n_in, const void* 
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
                           const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
-                          void* workspace, size_t workspace_bytes, htr_stream_t stream, void* const* peer_y = nullptr, int npeer = 0);
+                          void* workspace, size_t workspace_bytes, htr_stream_t stream, void* const* peer_y = nullptr, int npeer = 0,
+                          int share = 1);
 
 
 const char* htr_status_string(int status) {
@@ -525,16 +526,16 @@ int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride,
 
 int htr_linear_routed_peers(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count, int table_rows,
                             const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
-                            const uint8_t* const* sv_table, int mt, int nt, int K, void* y, void* const* peer_y, int npeer, int prologue,
-                            void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+                            const uint8_t* const* sv_table, int mt, int nt, int K, void* y, void* const* peer_y, int npeer, int share,
+                            int prologue, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
   if (count > 0 && (!x || !y || !route)) return HTR_ERR_NULL;
-  if (npeer < 1 || !peer_y) return HTR_ERR_BAD_SHAPE;
+  if (npeer < 0 || npeer > 8 || (npeer > 0 && !peer_y) || share < 1 || share > 64) return HTR_ERR_BAD_SHAPE;
   if (x_div < 1 || x_row_stride < 0 || table_rows < 1 || (prologue != HTR_PROLOGUE_NONE && prologue != HTR_PROLOGUE_SWIGLU))
     return HTR_ERR_BAD_SHAPE;
   if (prologue == HTR_PROLOGUE_SWIGLU && dtype != HTR_DTYPE_BF16) return HTR_ERR_BAD_DTYPE;
   if (count > 0 && (!aligned16(x) || !aligned16(y))) return HTR_ERR_ALIGNMENT;
   return launch_grouped(nullptr, nullptr, x, y, x_div, x_row_stride, route, table_rows, prologue, dtype, qweight_table, mt, nt, K, scales_table, su_table,
-                        sv_table, count, workspace, workspace_bytes, stream, peer_y, npeer);
+                        sv_table, count, workspace, workspace_bytes, stream, peer_y, npeer, share);
 }
 
 // shared body of the grouped entry points: per-problem pointer lists (x_list / y_list), or a route into per-expert tables with the
@@ -542,7 +543,7 @@ int htr_linear_routed_peers(const void* x, int dtype, int x_div, int64_t x_row_s
 static int launch_grouped(const void* const* x_list, void* const* y_list, const void* x, void* y, int x_div, int64_t x_row_stride,
                           const int64_t* route, int table_rows, int prologue, int dtype, const void* const* qweight_list, int mt, int nt, int K,
                           const void* const* scales_list, const uint8_t* const* su_list, const uint8_t* const* sv_list, int count,
-                          void* workspace, size_t workspace_bytes, htr_stream_t stream, void* const* peer_y, int npeer) {
+                          void* workspace, size_t workspace_bytes, htr_stream_t stream, void* const* peer_y, int npeer, int share) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (count < 0 || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
@@ -560,7 +561,9 @@ static int launch_grouped(const void* const* x_list, void* const* y_list, const 
   const int per_sm = cached_occupancy(dev, K, 1);
   const long long cap = (long long)sms * per_sm;
   const long long rbs = (long long)count * rbp;
-  long long split = cap / rbs;
+  // `share`: only one problem in `share` has its weights here (expert parallelism: the thread blocks of the others leave at once),
+  // so the grid is made that many times larger than the GPU
+  long long split = cap * (share < 1 ? 1 : share) / rbs;
   if (split < 1) split = 1;
   if (split > pl.cg) split = pl.cg;
   const size_t need = counter_bytes(m) + (size_t)rbs * (size_t)split * 128 * sizeof(float);

@@ -254,7 +254,7 @@ def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K
     _lib.check(rc, "htr_linear_grouped")
 
 
-def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, out=None, peer_ptrs=None):
+def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, out=None, peer_ptrs=None, share=1):
     """One launch over `route.numel()` problems (htr_linear_routed): problem i multiplies activation row i // x_div of `x` by the
     packed matrix whose four tensor addresses sit in row route[i] of `tables` (four int64 CUDA tensors, one row per expert; a
     zero weight address, or a route entry outside the tables, skips the problem) and writes row i of the result [count, m].  With prologue=PROLOGUE_SWIGLU the rows of
@@ -273,18 +273,19 @@ def linear_routed(x, route, tables, mt, nt, K, x_div=1, prologue=PROLOGUE_NONE, 
     with torch.cuda.device(dev):
         ws = workspace(dev, need)
         st = torch.cuda.current_stream(dev).cuda_stream
-        if peer_ptrs is None:
+        if peer_ptrs is None and share <= 1:
             rc = _lib.lib.htr_linear_routed(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count, int(tables[0].numel()),
                                             tables[0].data_ptr(), tables[1].data_ptr(), tables[2].data_ptr(), tables[3].data_ptr(), mt, nt, K,
                                             out.data_ptr(), int(prologue), ws.data_ptr(), ws.numel(), st)
         else:
             import ctypes
 
-            host = (ctypes.c_void_p * len(peer_ptrs))(*[int(v) for v in peer_ptrs])
+            peers = [] if peer_ptrs is None else [int(v) for v in peer_ptrs]
+            host = (ctypes.c_void_p * max(len(peers), 1))(*peers)
             rc = _lib.lib.htr_linear_routed_peers(x.data_ptr(), _DTYPES[x.dtype], int(x_div), x.shape[1], route.data_ptr(), count,
                                                   int(tables[0].numel()), tables[0].data_ptr(), tables[1].data_ptr(), tables[2].data_ptr(),
-                                                  tables[3].data_ptr(), mt, nt, K, out.data_ptr(), host, len(host), int(prologue),
-                                                  ws.data_ptr(), ws.numel(), st)
+                                                  tables[3].data_ptr(), mt, nt, K, out.data_ptr(), host if peers else None, len(peers),
+                                                  int(share), int(prologue), ws.data_ptr(), ws.numel(), st)
         _lib.check(rc, "htr_linear_routed")
     return out
 

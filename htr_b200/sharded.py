@@ -243,6 +243,11 @@ class ExpertParallelMoE:
         self._tables = None
         self._peer = None
         self._rows = {}
+        # Plan the routed launches for the share of the pairs whose expert lives here (world times more thread blocks than the GPU
+        # holds; those of the other ranks' pairs leave at once).  The float32 partial sums of a row then add up in another order
+        # than on one GPU: every rank still holds the same bits (a row is computed once, by its owner), equal to the single-GPU
+        # layer to float32 rounding.  False keeps the single-GPU plan and with it equality with the single-GPU layer bit for bit.
+        self.plan_for_share = True
 
     def _address_tables(self, dev):
         """int64 device tensors [all experts] with the addresses of each expert's wire tensors (for the grouped kernel);
@@ -301,19 +306,22 @@ class ExpertParallelMoE:
         skip = self.world > 1 and not exchange                          # rows of skipped pairs must read as zero
         alloc = torch.zeros if skip else torch.empty
         # (with `exchange`, the gate_up rows of pairs owned elsewhere are never read: the down launch skips the same pairs)
-        gu = ops.linear_routed(x, route, tabs["gate_up"], mt_gu, nt_gu, K, x_div=k, out=alloc(T * k, mt_gu * 16, dtype=x.dtype, device=dev))
+        share = self.world if (x.is_cuda and self.plan_for_share) else 1  # one pair in `world` has its expert here
+        gu = ops.linear_routed(x, route, tabs["gate_up"], mt_gu, nt_gu, K, x_div=k, out=alloc(T * k, mt_gu * 16, dtype=x.dtype, device=dev),
+                               share=share)
         if x.dtype == torch.bfloat16:
             act, prologue = gu, ops.PROLOGUE_SWIGLU
         else:
             inter = mt_gu * 8
             act, prologue = (torch.nn.functional.silu(gu[:, :inter]) * gu[:, inter:]).contiguous(), ops.PROLOGUE_NONE
         if not exchange:
-            return ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=alloc(T * k, mt_dn * 16, dtype=x.dtype, device=dev))
+            return ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=alloc(T * k, mt_dn * 16, dtype=x.dtype, device=dev),
+                                     share=share)
         ex = self._row_exchange(T * k, mt_dn * 16, x.dtype, dev)
         half = ex["flip"]
         ex["flip"] ^= 1
         dn = ex["buf"][half, :T * k]
-        ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=dn, peer_ptrs=ex["ptrs"][half])
+        ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=dn, peer_ptrs=ex["ptrs"][half], share=share)
         ex["hdl"].barrier(channel=0)
         return dn
 
@@ -412,7 +420,8 @@ class ExpertParallelMoE:
     def __call__(self, x, topk_ids, topk_w, grouped=None, combine=None):
         """combine (several ranks, CUDA, grouped form, NCCL group; default "rows" where it applies):
         "rows" = the down launch stores each pair's row into every rank, one barrier, then the same weighted sum as on one GPU
-                 (the result equals the single-GPU one bit for bit; up to 4096 pairs);
+                 (every rank holds the same bits; with plan_for_share = False they equal the single-GPU result bit for bit; up to
+                 4096 pairs);
         "peer" = peer stores of the ranks' float32 partial sums + rank-ordered add (up to 64 tokens);
         "nccl" = all-gather of the float32 parts + rank-ordered add."""
         use_grouped = (x.is_cuda and self.count > 0) if grouped is None else grouped

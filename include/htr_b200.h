@@ -166,15 +166,19 @@ int htr_linear_routed(const void* x, int dtype, int x_div, int64_t x_row_stride,
                       const uint8_t* const* sv_table, int mt, int nt, int K, void* y, int prologue, void* workspace,
                       size_t workspace_bytes, htr_stream_t stream);
 
-/* htr_linear_routed for expert parallelism on one NVLink box: the output row of every problem this rank owns (non-NULL weight entry)
- * is stored, with plain peer stores, into the matrix of each peer at the byte offset it has in y (peer_y[i]: the peers' [count][m]
- * matrices as mapped into this process, this rank's own among them; y itself is only the base the offsets are taken from and is not
- * written).  After the ranks have ordered themselves (a barrier across them) every rank holds the rows of all problems, each
- * computed by the rank that owns its expert, and combines them exactly as a single GPU would.  (No counterpart in the reference.) */
+/* htr_linear_routed for expert parallelism on one NVLink box.
+ * share: this rank holds the weights of about one problem in `share` (the number of ranks the experts are dealt to); the launch is
+ * planned with that many times more thread blocks than the GPU holds, because those of the other ranks' problems leave at once.
+ * npeer > 0: the output row of every problem this rank owns (non-NULL weight entry) is stored, with plain peer stores, into the
+ * matrix of each peer at the byte offset it has in y (peer_y[i]: the peers' [count][m] matrices as mapped into this process, this
+ * rank's own among them; y itself is then only the base the offsets are taken from and is not written).  After the ranks have
+ * ordered themselves (a barrier across them) every rank holds the rows of all problems, each computed by the rank that owns its
+ * expert, and combines them exactly as a single GPU would.  npeer == 0: rows go to y as in htr_linear_routed.
+ * (No counterpart in the reference.) */
 int htr_linear_routed_peers(const void* x, int dtype, int x_div, int64_t x_row_stride, const int64_t* route, int count, int table_rows,
                             const void* const* qweight_table, const void* const* scales_table, const uint8_t* const* su_table,
-                            const uint8_t* const* sv_table, int mt, int nt, int K, void* y, void* const* peer_y, int npeer, int prologue,
-                            void* workspace, size_t workspace_bytes, htr_stream_t stream);
+                            const uint8_t* const* sv_table, int mt, int nt, int K, void* y, void* const* peer_y, int npeer, int share,
+                            int prologue, void* workspace, size_t workspace_bytes, htr_stream_t stream);
 
 /* Padded form (the reference's HTRHCLinearMethod.apply, htr/vllm_plugin.py:313-326: F.pad of the input to n_pad, slice of
  * the output to m_out, both as separate copies there): the stored tensors cover a padded [m = 16*mt, n = 16*nt] matrix, x has

@@ -257,6 +257,13 @@ def test_routed_launch_equals_one_call_per_problem(dev, K):
         if e != 3:
             want = ops.linear_fused(gu[i:i + 1].contiguous(), *experts[e], prologue=ops.PROLOGUE_SWIGLU)
             assert torch.equal(got[i:i + 1], want)
+    # planned for a rank that owns one problem in four (htr_linear_routed_peers without peers: four times the thread blocks, other
+    # column splits): the same rows to float32 rounding, absent experts untouched
+    x = torch.randn(T, n, device=dev)
+    base = ops.linear_routed(x, route, tables, m // 16, n // 16, K, x_div=k, out=torch.full((T * k, m), 7.0, device=dev))
+    wide = ops.linear_routed(x, route, tables, m // 16, n // 16, K, x_div=k, out=torch.full((T * k, m), 7.0, device=dev), share=4)
+    assert bool((wide[4] == 7.0).all())
+    assert float((wide - base).norm() / base.norm()) <= 2e-6
     # route entries outside the tables are skipped like absent experts (the kernel compares them with the table length first)
     wild = torch.tensor([0, E, 2, -1, 3, 1], dtype=torch.int64, device=dev)
     x = torch.randn(T, n, device=dev)

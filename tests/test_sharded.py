@@ -204,8 +204,16 @@ def _nccl_worker(rank, world, port, q):
             g = dist.new_group([r])
             solo = g if r == rank else solo
         one = ExpertParallelMoE(experts, device=dev, group=solo)
+        moe.plan_for_share = False                                           # the single-GPU launch plan: bit for bit
         for xin in (xm, xm.bfloat16(), xm * 2):
             ok = ok and bool(torch.equal(moe(xin.to(dev), ids, w), one(xin.to(dev), ids, w)))
+        moe.plan_for_share = True                                            # the default: more thread blocks per owned pair,
+        for xin in (xm, xm.bfloat16()):                                      # float32 partial sums in another order
+            a, b = moe(xin.to(dev), ids, w).float(), one(xin.to(dev), ids, w).float()
+            ok = ok and float((a - b).norm() / b.norm()) <= (1e-6 if xin.dtype == torch.float32 else 4e-3)
+            g = [torch.empty_like(a) for _ in range(world)]
+            dist.all_gather(g, a)
+            ok = ok and all(bool(torch.equal(t, a)) for t in g)             # every rank holds the same bits
         # the other two combines (float32 partial sums by peer stores, or by all-gather; rank-ordered add) agree to rounding
         y_nccl = moe(xm.to(dev), ids, w, combine="nccl").float().cpu()
         ok = ok and float((y_grp - y_nccl).norm() / y_nccl.norm()) <= 1e-6
