@@ -242,7 +242,8 @@ def lm_head_record(torch, dist, rank, world, dev, reps):
     sharded = [RowShardedLinear(*w, device=dev, gather="peer" if world > 1 else "nccl") for w in packed]
     single = [RowShardedLinear(*w, device=dev, group=solo) for w in packed] if world > 1 else sharded
     out = {"workload": "lm_head_151936x4096_K4_row_sharded",
-           "gather": "batch 1: epilogue peer stores + one cross-rank barrier; batch 8: local tensor-core GEMM + NCCL all-gather" if world > 1 else "none"}
+           "gather": ("batch 1: epilogue peer stores + one cross-rank barrier kernel of the library (htr_peer_barrier); "
+                      "batch 8: local tensor-core GEMM + NCCL all-gather") if world > 1 else "none"}
     for M in (1, 8):
         x = torch.randn(M, n, device=dev, generator=torch.Generator(device=dev).manual_seed(M)).bfloat16()
         if world > 1:
@@ -263,9 +264,11 @@ def lm_head_record(torch, dist, rank, world, dev, reps):
             out[f"batch{M}"]["shard_kernel_only_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h.local(x) for h in sharded], reps, calls=2) / copies, 2)
             if M == 1:
                 from htr_b200 import sharded as sharded_mod
-                sharded_mod.PEER_ORDER = "flags"
-                out[f"batch{M}"]["with_delivery_flags_us"] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps, calls=2) / copies, 2)
-                sharded_mod.PEER_ORDER = "barrier"
+                default_order = sharded_mod.PEER_ORDER
+                for order, key in (("flags", "with_delivery_flags_us"), ("barrier", "with_torch_symm_barrier_us")):
+                    sharded_mod.PEER_ORDER = order
+                    out[f"batch{M}"][key] = round(1e3 * _time_graph(torch, dist, world, dev, lambda: [h(x) for h in sharded], reps, calls=2) / copies, 2)
+                sharded_mod.PEER_ORDER = default_order
     if world > 1:
         out["gather_check"] = "batch 1: bit-identical to the single-GPU result; batch 8: within bf16 rounding (4e-3 norm-relative)"
     return out
@@ -457,7 +460,10 @@ def run_ours(args):
     gather_mode = os.environ.get("HTR_BENCH_GATHER", "peer") if world > 1 else "none"
     hdl = None
     flags = flag_ptrs = epoch = wait_status = None
-    peer_order = os.environ.get("HTR_BENCH_PEER_ORDER", "barrier")    # "flags": delivery flags raised by the kernels + one bounded wait per K-group
+    # how the ranks order themselves after a K-group: "kernel" = the library's barrier kernel, "barrier" = torch symmetric memory's,
+    # "flags" = delivery flags raised by the kernels + one bounded wait
+    peer_order = os.environ.get("HTR_BENCH_PEER_ORDER", "kernel")
+    rank_barrier = None
     if gather_mode == "peer":
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
@@ -479,6 +485,10 @@ def run_ours(args):
         flag_ptrs = [int(p) + 4 * rank for p in fh.buffer_ptrs]
         epoch = torch.zeros(1, dtype=torch.int32, device=dev)
         wait_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        if peer_order == "kernel":
+            from htr_b200.sharded import RankBarrier
+            rank_barrier = RankBarrier(world, rank, dev)
+            wait_status = rank_barrier.status
         torch.cuda.synchronize()
         dist.barrier()
 
@@ -509,6 +519,8 @@ def run_ours(args):
             # the timed passes, so a rank that runs ahead may already overwrite them for the next pass)
             if peer_order == "flags":
                 ops.peer_wait(flags, epoch, world, wait_status, count=len(items))
+            elif peer_order == "kernel":
+                rank_barrier()
             else:
                 hdl.barrier(channel=0)
             outs = [it["gathered"][rank] for it in items]

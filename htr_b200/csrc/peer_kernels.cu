@@ -38,6 +38,33 @@ __global__ void peer_wait_kernel(const unsigned* __restrict__ flags, unsigned* _
   if (lane == 0) *epoch = want;
 }
 
+// Barrier across the ranks of one NVLink box, as one small kernel per rank: lane r adds 1 to this rank's word in rank r's flag array
+// (system scope, after a system-wide fence) and then waits, bounded, until rank r has done the same here.  The kernel is launched
+// so that it may become resident while its predecessor still runs (programmatic stream serialisation) and begins with
+// griddepcontrol.wait: what this rank stored before the barrier -- peer stores of the preceding kernel included -- is complete and
+// flushed when the first signal leaves, and the launch latency is hidden behind the predecessor.
+__global__ void peer_barrier_kernel(unsigned* const* __restrict__ peer_word, const unsigned* __restrict__ flags, unsigned* __restrict__ epoch,
+                                    int nranks, int* __restrict__ status, unsigned limit) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int lane = threadIdx.x;
+  const unsigned want = *epoch + 1u;
+  if (lane < nranks) {
+    __threadfence_system();
+    atomicAdd_system(peer_word[lane], 1u);
+    bool ok = false;
+    for (unsigned it = 0; it < limit; ++it) {
+      if ((int)(load_acquire_sys(flags + lane) - want) >= 0) {
+        ok = true;
+        break;
+      }
+      __nanosleep(it < 256 ? 20 : 256);
+    }
+    if (!ok && status) atomicOr(status, 1 << lane);     // rank `lane` did not arrive in time
+  }
+  __syncwarp();
+  if (lane == 0) *epoch = want;
+}
+
 // part[t, :] = sum_j w[t, j] * dn[t * k + j, :] (float32), stored into every peer's buffer at [my_rank][t][:]; then the signal.
 // grid (h / 1024, T), 256 threads, four columns per thread.
 __global__ void __launch_bounds__(256) moe_combine_peers_kernel(const void* __restrict__ dn, int dtype, const float* __restrict__ w, int k, int h,
@@ -105,6 +132,22 @@ int htr_peer_wait(const unsigned* flags, unsigned* epoch, int nranks, int count,
   // about two seconds at the longest: 2^23 polls a quarter of a microsecond apart
   peer_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flags, epoch, nranks, (unsigned)count, status, 1u << 23);
   return cudaGetLastError() == cudaSuccess ? HTR_OK : HTR_ERR_CUDA;
+}
+
+int htr_peer_barrier(unsigned* const* peer_word, const unsigned* flags, unsigned* epoch, int nranks, int* status, htr_stream_t stream) {
+  if (!peer_word || !flags || !epoch) return HTR_ERR_NULL;
+  if (nranks < 1 || nranks > 32) return HTR_ERR_BAD_SHAPE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // about two seconds at the longest
+  return cudaLaunchKernelEx(&cfg, peer_barrier_kernel, peer_word, flags, epoch, nranks, status, 1u << 23) == cudaSuccess ? HTR_OK : HTR_ERR_CUDA;
 }
 
 int htr_moe_combine_peers(const void* dn, int dtype, const float* gates, int tokens, int top_k, int hidden, float* const* peer_out, int npeer,

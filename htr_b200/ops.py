@@ -238,6 +238,16 @@ def peer_wait(flags, epoch, nranks, status=None, count=1):
     _lib.check(rc, "htr_peer_wait")
 
 
+def peer_barrier(peer_words, flags, epoch, nranks, status=None):
+    """Barrier across the ranks of one NVLink box on the current stream (htr_peer_barrier: one small kernel per rank, bounded wait).
+    peer_words: int64 CUDA tensor [nranks] with the address of this rank's word in every rank's flag array; flags: int32 CUDA
+    tensor (this GPU's words); epoch / status: int32 CUDA tensors [1]."""
+    st = torch.cuda.current_stream(flags.device).cuda_stream
+    rc = _lib.lib.htr_peer_barrier(peer_words.data_ptr(), flags.data_ptr(), epoch.data_ptr(), int(nranks),
+                                   None if status is None else status.data_ptr(), st)
+    _lib.check(rc, "htr_peer_barrier")
+
+
 def linear_grouped(x_ptrs, qw_ptrs, sc_ptrs, su_ptrs, sv_ptrs, y_ptrs, mt, nt, K, dtype):
     """`count` packed linears of one shape in one launch, one activation row each (htr_linear_grouped).  Every argument is
     an int64 CUDA tensor of `count` device addresses (built on the device, e.g. by indexing per-expert address tables with

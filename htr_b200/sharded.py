@@ -20,12 +20,13 @@ import torch
 import torch.distributed as dist
 
 
-# How the ranks order themselves after peer stores: "barrier" = the producer kernel ends, then one cross-rank barrier kernel of
-# torch's symmetric memory (signal + wait on every peer); "flags" = the producer kernel raises delivery flags itself and the
-# consumer runs a bounded wait (htr_peer_wait).  Measured on 2 B200s the barrier form is the faster one (the flags need a
-# system-wide fence in every finishing thread block, which drains the SM's memory pipeline): 85.8 against 93.2 us for the
-# 151936x4096 head at batch 1, 3632 against 2910 GB/s on the weak-scaled MLP sweep.
-PEER_ORDER = "barrier"
+# How the ranks order themselves after peer stores:
+#   "kernel"  = the producer kernel ends, then htr_peer_barrier: one small kernel per rank that becomes resident behind the producer,
+#               raises this rank's word in every rank's flag array and waits (bounded) for every rank's word here;
+#   "barrier" = the same with the barrier kernel of torch's symmetric memory;
+#   "flags"   = the producer kernel raises the delivery flags itself (its last thread block) and the consumer runs a bounded wait
+#               (htr_peer_wait).
+PEER_ORDER = "kernel"
 
 
 def row_block_partition(m, world):
@@ -91,6 +92,40 @@ def all_gather_rows(y_local, group=None):
     return torch.stack(parts)
 
 
+class RankBarrier:
+    """Barrier across the ranks of one NVLink box as one small kernel per rank (htr_peer_barrier): flag words in symmetric memory,
+    word r of a rank's array is raised by rank r; the count of barriers passed lives in device memory (CUDA-graph replay keeps it)."""
+
+    def __init__(self, world, rank, device, group=None):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")     # plain peer stores and atomics only
+        import torch.distributed._symmetric_memory as symm_mem
+
+        grp = group if group is not None else dist.group.WORLD
+        self.world = world
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        self.hdl = symm_mem.rendezvous(self.flags, grp)
+        self.peer_words = torch.tensor([int(p) + 4 * rank for p in self.hdl.buffer_ptrs], dtype=torch.int64, device=device)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)              # bit r: rank r did not arrive in time
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)                                                      # every rank's words are zero before anyone signals
+
+    def __call__(self):
+        from . import ops
+
+        ops.peer_barrier(self.peer_words, self.flags, self.epoch, self.world, self.status)
+
+    def check(self):
+        """Host-side check (synchronises): raises if a bounded wait ran out since the last check."""
+        missed = int(self.status.item())
+        if missed:
+            self.status.zero_()
+            raise RuntimeError(f"cross-rank barrier timed out waiting for ranks {[r for r in range(self.world) if missed >> r & 1]}")
+
+
 class PeerGather:
     """Gather buffers in symmetric memory: every rank maps every rank's buffer, so a kernel can store its output rows
     straight into all of them over NVLink (htr_linear_peers) and no collective kernel runs.  The ranks then order themselves
@@ -116,6 +151,7 @@ class PeerGather:
         self.flags.zero_()
         self.flag_hdl = symm_mem.rendezvous(self.flags, grp)
         self.flag_ptrs = [int(p) + 4 * rank for p in self.flag_hdl.buffer_ptrs]     # this rank's word in every rank's array
+        self.rank_barrier = RankBarrier(world, rank, device, group)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)              # bit r: rank r missed a bounded wait
         torch.cuda.synchronize(device)
@@ -134,7 +170,11 @@ class PeerGather:
         ops.peer_wait(self.flags, self.epoch, self.world, self.status, count)
 
     def barrier(self):
-        self.hdl.barrier(channel=0)
+        """Order the ranks after peer stores that carried no delivery signal (PEER_ORDER "kernel" or "barrier")."""
+        if PEER_ORDER == "barrier":
+            self.hdl.barrier(channel=0)
+        else:
+            self.rank_barrier()
 
     def check(self):
         """Host-side check (synchronises): raises if a bounded wait ran out since the last check."""
@@ -142,6 +182,7 @@ class PeerGather:
         if missed:
             self.status.zero_()
             raise RuntimeError(f"peer delivery wait timed out for ranks {[r for r in range(self.world) if missed >> r & 1]}")
+        self.rank_barrier.check()
 
     def result(self, rows):
         out = self.buf[self.flip, :, :rows, :]
@@ -278,7 +319,7 @@ class ExpertParallelMoE:
             hdl = symm_mem.rendezvous(buf, grp)
             half_bytes = cap * hdim * buf.element_size()
             ptrs = [[int(p) + hf * half_bytes for p in hdl.buffer_ptrs] for hf in (0, 1)]
-            ex = dict(pairs=cap, buf=buf, hdl=hdl, ptrs=ptrs, flip=0)
+            ex = dict(pairs=cap, buf=buf, hdl=hdl, ptrs=ptrs, flip=0, barrier=RankBarrier(self.world, self.rank, dev, self.group))
             torch.cuda.synchronize(dev)
             dist.barrier(group=grp)
             self._rows[key] = ex
@@ -322,7 +363,10 @@ class ExpertParallelMoE:
         ex["flip"] ^= 1
         dn = ex["buf"][half, :T * k]
         ops.linear_routed(act, route, tabs["down"], mt_dn, nt_dn, K, prologue=prologue, out=dn, peer_ptrs=ex["ptrs"][half], share=share)
-        ex["hdl"].barrier(channel=0)
+        if PEER_ORDER == "barrier":
+            ex["hdl"].barrier(channel=0)
+        else:
+            ex["barrier"]()
         return dn
 
     @staticmethod

@@ -114,6 +114,14 @@ int htr_linear_peers_signal(const void* x, int dtype, int M, const void* qweight
  * survives CUDA-graph replay).  The wait is bounded (about two seconds); a producer that has not delivered by then gets its bit
  * set in *status (device int, may be NULL) and the kernel returns: the buffer then holds stale rows. */
 int htr_peer_wait(const unsigned* flags, unsigned* epoch, int nranks, int count, int* status, htr_stream_t stream);
+/* Barrier across the ranks of one NVLink box as one small kernel per rank (no collective library): peer_word[r] = the address, as
+ * mapped into this process, of THIS rank's word in rank r's flag array (a DEVICE array of nranks pointers, this rank's own
+ * included); flags = this GPU's flag array (word r is raised by rank r); *epoch = barriers passed so far (device memory: survives
+ * CUDA-graph replay).  The kernel first waits for everything launched before it on `stream` (peer stores of the preceding kernel are
+ * complete and flushed then), raises its word everywhere and waits until every rank has raised its word here.  The wait is bounded
+ * (about two seconds): a rank that has not arrived by then gets its bit set in *status (device int, may be NULL) and the kernel
+ * returns.  The flag words must be used by nothing else (they count barriers since they were zeroed). */
+int htr_peer_barrier(unsigned* const* peer_word, const unsigned* flags, unsigned* epoch, int nranks, int* status, htr_stream_t stream);
 /* Combine step of an expert-parallel mixture-of-experts layer without a collective: part[t, :] = sum_j gates[t, j] *
  * dn[t * top_k + j, :] (float32) is stored into every peer's buffer at float offset slot_offset (+ t * hidden), with the same
  * delivery signal as above when peer_flag is given (done_counter: a zeroed device int of this rank); htr_rank_sum then adds the

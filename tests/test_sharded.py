@@ -172,7 +172,7 @@ def _nccl_worker(rank, world, port, q):
         from htr_b200 import sharded as sharded_mod
 
         peer = RowShardedLinear(qw, sc, su, sv, device=dev, gather="peer")
-        for order in ("barrier", "flags"):                                   # both ways of ordering the ranks after the peer stores
+        for order in ("kernel", "barrier", "flags"):                         # the three ways of ordering the ranks after the peer stores
             sharded_mod.PEER_ORDER = order
             for i in range(3):
                 xi = (x[:1 + i % 2] * (i + 1)).contiguous()
@@ -180,7 +180,7 @@ def _nccl_worker(rank, world, port, q):
                     want = ops.linear(xi, *full_w)
                 ok = ok and bool(torch.equal(peer(xi), want))
         peer.peer.check()                                                    # no bounded wait ran out
-        sharded_mod.PEER_ORDER = "barrier"
+        sharded_mod.PEER_ORDER = "kernel"
         # three rows (float32 sums per window): within bf16 rounding of the single-GPU result; eight rows: local GEMM + all-gather
         for rows in (3, 8):
             xr = torch.randn(rows, 1024, generator=torch.Generator().manual_seed(rows)).bfloat16().to(dev)
@@ -208,6 +208,7 @@ def _nccl_worker(rank, world, port, q):
         for xin in (xm, xm.bfloat16(), xm * 2):
             ok = ok and bool(torch.equal(moe(xin.to(dev), ids, w), one(xin.to(dev), ids, w)))
         moe.plan_for_share = True                                            # the default: more thread blocks per owned pair,
+        y_rows = moe(xm.to(dev), ids, w)
         for xin in (xm, xm.bfloat16()):                                      # float32 partial sums in another order
             a, b = moe(xin.to(dev), ids, w).float(), one(xin.to(dev), ids, w).float()
             ok = ok and float((a - b).norm() / b.norm()) <= (1e-6 if xin.dtype == torch.float32 else 4e-3)
@@ -222,7 +223,11 @@ def _nccl_worker(rank, world, port, q):
         for order in ("barrier", "flags", "barrier"):
             sharded_mod.PEER_ORDER = order
             ok = ok and bool(torch.equal(moe(xm.to(dev), ids, w, combine="peer").float().cpu(), y_peer))
-        sharded_mod.PEER_ORDER = "barrier"
+        sharded_mod.PEER_ORDER = "barrier"                                   # the row exchange under torch's barrier as well
+        ok = ok and bool(torch.equal(moe(xm.to(dev), ids, w), y_rows))
+        sharded_mod.PEER_ORDER = "kernel"
+        for ex in moe._rows.values():
+            ex["barrier"].check()
         ok = ok and int(moe._peer["status"].item()) == 0
         torch.cuda.synchronize()
         q.put((rank, ok, tuple(y.shape)))
@@ -245,6 +250,31 @@ def test_two_nccl_ranks_match_single_gpu_bit_for_bit():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert all(ok and shape == (2, 128 * 11) for _, ok, shape in res)
+
+
+@pytest.mark.gpu
+def test_peer_barrier_gives_up_and_reports_the_missing_rank():
+    """The library's cross-rank barrier kernel waits with a bound: emulated on one GPU as rank 0 of two, with a peer whose word
+    nothing raises, it returns after about two seconds, sets the missing rank's bit and leaves the context usable; once the
+    peer's word is there the next barrier passes at once."""
+    from htr_b200 import ops
+
+    dev = torch.device("cuda:0")
+    flags = torch.zeros(64, dtype=torch.int32, device=dev)                  # this GPU's words: word 0 = rank 0 (itself), word 1 = rank 1
+    elsewhere = torch.zeros(64, dtype=torch.int32, device=dev)              # stands for rank 1's flag array
+    words = torch.tensor([flags.data_ptr(), elsewhere.data_ptr()], dtype=torch.int64, device=dev)
+    epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.peer_barrier(words, flags, epoch, 2, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0b10 and int(epoch.item()) == 1
+    assert int(flags[0].item()) == 1 and int(elsewhere[0].item()) == 1      # its own word was raised in both arrays
+    flags[1] = 2                                                            # rank 1 arrives at barrier 2
+    status.zero_()
+    ops.peer_barrier(words, flags, epoch, 2, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(epoch.item()) == 2
+    assert float(torch.ones(4, device=dev).sum()) == 4.0                    # the device still answers
 
 
 @pytest.mark.gpu
