@@ -243,7 +243,7 @@ def lm_head_record(torch, dist, rank, world, dev, reps):
     single = [RowShardedLinear(*w, device=dev, group=solo) for w in packed] if world > 1 else sharded
     out = {"workload": "lm_head_151936x4096_K4_row_sharded",
            "gather": ("batch 1: epilogue peer stores + one cross-rank barrier kernel of the library (htr_peer_barrier); "
-                      "batch 8: local tensor-core GEMM + NCCL all-gather") if world > 1 else "none"}
+                      "batch 8: the tensor-core GEMM with the same peer-store epilogue and barrier") if world > 1 else "none"}
     for M in (1, 8):
         x = torch.randn(M, n, device=dev, generator=torch.Generator(device=dev).manual_seed(M)).bfloat16()
         if world > 1:

@@ -17,7 +17,7 @@ INPUT_INDEPENDENT = 1
 EXACT_SUMS = 2
 
 EXPORTS = ("htr_status_string", "htr_last_cuda_error", "htr_version", "htr_decode_raw", "htr_rht",
-           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_peers", "htr_linear_grouped", "htr_linear_grouped_workspace_bytes", "htr_linear_routed", "htr_linear_static", "htr_linear_padded", "htr_linear_fused", "htr_linear_gemm", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_linear_gemm_last_cuda_error", "htr_dequant_w", "htr_viterbi", "htr_viterbi_workspace_bytes", "htr_viterbi_last_cuda_error", "htr_codebook_f32",
+           "htr_linear_workspace_bytes", "htr_linear_counter_bytes", "htr_linear", "htr_linear_ex", "htr_linear_peers", "htr_linear_grouped", "htr_linear_grouped_workspace_bytes", "htr_linear_routed", "htr_linear_static", "htr_linear_padded", "htr_linear_fused", "htr_linear_gemm", "htr_linear_gemm_peers", "htr_linear_gemm_workspace_bytes", "htr_linear_gemm_error_offset", "htr_linear_gemm_last_cuda_error", "htr_dequant_w", "htr_viterbi", "htr_viterbi_workspace_bytes", "htr_viterbi_last_cuda_error", "htr_codebook_f32",
            "htr_linear_plan", "htr_set_gemv_kernel", "htr_linear_fault_offset", "htr_linear_peers_signal", "htr_linear_routed_peers", "htr_peer_wait", "htr_peer_barrier", "htr_moe_combine_peers", "htr_moe_weighted_sum", "htr_rank_sum", "htr_dec_add_rmsnorm", "htr_dec_rope_cache", "htr_dec_attention",
            "htr_dec_swiglu", "htr_dec_rope_attention")
 
@@ -57,6 +57,7 @@ def _load():
     lib.htr_codebook_f32.argtypes = [vp, vp]
     lib.htr_linear_fused.argtypes = [vp, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, sz, vp, i32, vp, ctypes.c_float, i32]
     lib.htr_linear_gemm.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.htr_linear_gemm_peers.argtypes = [vp, i32, i32, vp, i32, i32, i32, vp, vp, vp, vp, ctypes.POINTER(vp), i32, i64, vp, sz, vp]
     lib.htr_linear_gemm_workspace_bytes.restype = sz
     lib.htr_linear_gemm_workspace_bytes.argtypes = [i32, i32, i32, i32]
     lib.htr_linear_gemm_error_offset.restype = sz

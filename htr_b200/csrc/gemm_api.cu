@@ -217,14 +217,37 @@ size_t htr_linear_gemm_workspace_bytes(int M, int m, int n, int K) {
   return b1 > b2 ? b1 : b2;
 }
 
+static int gemm_launch(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                       const uint8_t* sv, const void* bias, void* y, void* const* peer_y, int npeer, int64_t peer_offset, void* workspace,
+                       size_t workspace_bytes, htr_stream_t stream);
+
 int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
                     const uint8_t* sv, const void* bias, void* y, void* workspace, size_t workspace_bytes, htr_stream_t stream) {
+  return gemm_launch(x, dtype, M, qweight, mt, nt, K, scales, su, sv, bias, y, nullptr, 0, 0, workspace, workspace_bytes, stream);
+}
+
+int htr_linear_gemm_peers(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                          const uint8_t* sv, const void* bias, void* const* peer_y, int npeer, int64_t peer_offset, void* workspace,
+                          size_t workspace_bytes, htr_stream_t stream) {
+  if (npeer < 1 || npeer > 8 || !peer_y || peer_offset < 0 || (peer_offset & 7)) return HTR_ERR_BAD_SHAPE;
+  for (int i = 0; i < npeer; ++i)
+    if (!peer_y[i] || (reinterpret_cast<uintptr_t>(peer_y[i]) & 15u)) return peer_y[i] ? HTR_ERR_ALIGNMENT : HTR_ERR_NULL;
+  // a batch too wide for one launch would need the halves at different offsets: the row-shard form serves one launch
+  GemmPlan g;
+  if (M > 0 && width_ok(K) && mt > 0 && nt > 0 && make_gemm_plan(M, mt * 16, nt * 16, K, dtype == HTR_DTYPE_F32 ? 2 : 1, &g) != HTR_OK)
+    return HTR_ERR_TOO_LARGE;
+  return gemm_launch(x, dtype, M, qweight, mt, nt, K, scales, su, sv, bias, nullptr, peer_y, npeer, peer_offset, workspace, workspace_bytes, stream);
+}
+
+static int gemm_launch(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales, const uint8_t* su,
+                       const uint8_t* sv, const void* bias, void* y, void* const* peer_y, int npeer, int64_t peer_offset, void* workspace,
+                       size_t workspace_bytes, htr_stream_t stream) {
   if (!width_ok(K)) return HTR_ERR_BAD_K;
   if (dtype < HTR_DTYPE_BF16 || dtype > HTR_DTYPE_F32) return HTR_ERR_BAD_DTYPE;
   if (M < 0 || M > HTR_GEMM_MAX_ROWS || mt <= 0 || nt <= 0 || mt % 8 || nt % 8) return HTR_ERR_BAD_SHAPE;
   if (mt / 8 > (int)(kCounterRegion / 4)) return HTR_ERR_TOO_LARGE;
   if (M == 0) return HTR_OK;
-  if (!x || !qweight || !scales || !su || !sv || !y) return HTR_ERR_NULL;
+  if (!x || !qweight || !scales || !su || !sv || (!y && npeer == 0)) return HTR_ERR_NULL;
   const auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   if (!a16(x) || !a16(qweight) || !a16(y) || (bias && !a16(bias)) || !a16(workspace) || !a16(scales)) return HTR_ERR_ALIGNMENT;
   const int m = mt * 16, n = nt * 16;
@@ -232,7 +255,7 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
   const int planes = dtype == HTR_DTYPE_F32 ? 2 : 1;      // 16-bit activations need no lo plane
   if (planes == 2 && M > HTR_GEMM_MAX_ROWS_F32) return HTR_ERR_BAD_SHAPE;
   const int rc = make_gemm_plan(M, m, n, K, planes, &g);
-  if (rc == HTR_ERR_TOO_LARGE && M > 16) {                // too wide for one CTA's shared memory: two launches over row halves
+  if (rc == HTR_ERR_TOO_LARGE && M > 16 && npeer == 0) {  // too wide for one CTA's shared memory: two launches over row halves
     const int M1 = first_half_rows(M);
     const size_t esz = dtype == HTR_DTYPE_F32 ? 4 : 2;
     const int r1 = htr_linear_gemm(x, dtype, M1, qweight, mt, nt, K, scales, su, sv, bias, y, workspace, workspace_bytes, stream);
@@ -267,6 +290,9 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
   p.stages = g.stages;
   p.xsum_slices = gemm_rht_slices(g.np, n);
   p.cb = (float)codebook_scale();
+  p.npeer = npeer;
+  p.peer_offset = peer_offset;
+  for (int i = 0; i < 8; ++i) p.peer_y[i] = i < npeer ? peer_y[i] : nullptr;
   int e = run_rht_f16(x, dtype, M, g.np, n, planes, su, reinterpret_cast<__half*>(ws + g.off_xb), reinterpret_cast<float*>(ws + g.off_xsum),
                       reinterpret_cast<float*>(ws + g.off_tok), st);
   if (e) { t_gemm_cuda = e; return HTR_ERR_CUDA; }

@@ -92,7 +92,21 @@ struct GemmParams {
   int stages;             // stage pairs in the ring (2..kMaxStages)
   int xsum_slices;
   float cb;
+  // row-shard form: the output rows go, with plain peer stores, to element offset peer_offset + j * m + row of every buffer in
+  // peer_y (the gather buffers of all ranks of an NVLink box as mapped into this process) instead of y
+  void* peer_y[8];
+  int npeer;
+  long long peer_offset;
 };
+
+__device__ __forceinline__ void gemm_store_rows(const GemmParams& p, int j, int m, int row0, float4 o) {
+  if (p.npeer == 0) {
+    store_quad(p.y, (size_t)j * m + row0, p.dtype, o);
+  } else {
+#pragma unroll 1
+    for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)j * m + row0, p.dtype, o);
+  }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -450,7 +464,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
       float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
                              flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
       o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
-      store_quad(p.y, (size_t)j * m + row0, p.dtype, o);
+      gemm_store_rows(p, j, m, row0, o);
     }
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");   // nobody leaves while its shared memory may still be read
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -503,7 +517,7 @@ __global__ void __launch_bounds__(kGemmThreads) packed_gemm_tc_kernel(const Gemm
     float4 o = make_float4(flip(v[0] * kInvSqrt128, sv_bits & 1u), flip(v[1] * kInvSqrt128, (sv_bits >> 1) & 1u),
                            flip(v[2] * kInvSqrt128, (sv_bits >> 2) & 1u), flip(v[3] * kInvSqrt128, sv_bits >> 3));
     o.x += bias4.x; o.y += bias4.y; o.z += bias4.z; o.w += bias4.w;
-    store_quad(p.y, (size_t)j * m + row0, p.dtype, o);
+    gemm_store_rows(p, j, m, row0, o);
   }
 }
 

@@ -175,8 +175,9 @@ def linear_fused(x2, qweight, scales, su, sv, out=None, prologue=PROLOGUE_NONE, 
 _GEMM_WS = {}
 
 
-def _gemm(x2, qweight, scales, su, sv, bias, out):
-    """One C call of the tensor-core GEMM: up to 256 rows of x2 (128 for float32) against the packed weight."""
+def _gemm(x2, qweight, scales, su, sv, bias, out, peer_ptrs=None, elem_offset=0):
+    """One C call of the tensor-core GEMM: up to 256 rows of x2 (128 for float32) against the packed weight.  With peer_ptrs the
+    rows go to element offset `elem_offset` of every buffer in the list instead of `out` (htr_linear_gemm_peers)."""
     M = x2.shape[0]
     mt, nt, W = qweight.shape
     K = W // 8
@@ -189,9 +190,24 @@ def _gemm(x2, qweight, scales, su, sv, bias, out):
     if ws is None or ws.numel() < need:
         ws = torch.zeros(max(need, 1 << 24), dtype=torch.uint8, device=x2.device)
         _GEMM_WS[key] = ws
-    rc = _lib.lib.htr_linear_gemm(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
-                                  sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st)
+    if peer_ptrs is None:
+        rc = _lib.lib.htr_linear_gemm(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(), su.data_ptr(),
+                                      sv.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), st)
+    else:
+        import ctypes
+
+        arr = (ctypes.c_void_p * len(peer_ptrs))(*[int(p) for p in peer_ptrs])
+        rc = _lib.lib.htr_linear_gemm_peers(x2.data_ptr(), _DTYPES[x2.dtype], M, qweight.data_ptr(), mt, nt, K, scales.data_ptr(),
+                                            su.data_ptr(), sv.data_ptr(), None if bias is None else bias.data_ptr(), arr, len(peer_ptrs),
+                                            int(elem_offset), ws.data_ptr(), ws.numel(), st)
     _lib.check(rc, "htr_linear_gemm")
+
+
+def gemm_into_peers(x2, qweight, scales, su, sv, bias, peer_ptrs, elem_offset):
+    """Row-shard form of the tensor-core GEMM (5 .. 256 activation rows, one launch): the result rows [M, m_local] are stored, from
+    inside the kernel, at element offset `elem_offset` of every buffer in `peer_ptrs`; the caller orders the ranks afterwards."""
+    _check(x2, qweight, scales, su, sv, bias)
+    _gemm(x2, qweight, scales, su, sv, bias, None, peer_ptrs, elem_offset)
 
 
 def gemm_error_codes():

@@ -193,9 +193,9 @@ class PeerGather:
 class RowShardedLinear:
     """y = x @ W^T (+bias) with W's rows dealt to the ranks of `group`; every rank gets the full [.., m] result.
 
-    gather="nccl": all-gather of the local outputs.  gather="peer": the GEMV's epilogue stores its rows into every rank's
-    gather buffer itself and raises a delivery flag there (up to 4 activation rows; larger batches run the tensor-core GEMM
-    locally and all-gather its output)."""
+    gather="nccl": all-gather of the local outputs.  gather="peer": the kernel's epilogue stores its rows into every rank's
+    gather buffer itself (the GEMV up to 4 activation rows, the tensor-core GEMM up to 32) and one barrier kernel orders the ranks;
+    larger batches run the GEMM locally and all-gather its output."""
 
     def __init__(self, qweight, scales, su, sv, bias=None, group=None, device=None, linear_fn=None, gather="nccl", dtype=torch.bfloat16):
         self.group = group
@@ -211,7 +211,7 @@ class RowShardedLinear:
         self.linear_fn = linear_fn or _default_linear()
         self.peer = None
         if gather == "peer" and self.world > 1:
-            self.peer = PeerGather(self.world, self.rank, 8, self.qweight.shape[0] * 16, dtype, dev, group)
+            self.peer = PeerGather(self.world, self.rank, 32, self.qweight.shape[0] * 16, dtype, dev, group)
 
     def _exact(self):
         """Row shards must reproduce the unsharded rows whatever the shard count: up to four rows run on the integer-exact kernel."""
@@ -246,6 +246,16 @@ class RowShardedLinear:
             else:
                 self.peer.barrier()
             g = self.peer.result(x2.shape[0])                                # [world, M, rows_per_rank]
+            rows = x2.shape[0]
+        elif self.peer is not None and 4 < x2.shape[0] <= self.peer.max_rows and x2.dtype == self.peer.buf.dtype:
+            # the tensor-core GEMM's epilogue stores into every rank's gather buffer as well; one barrier orders the ranks
+            from . import ops
+
+            ptrs, off = self.peer.target()
+            bias = None if self.bias is None else self.bias.to(x2.dtype)
+            ops.gemm_into_peers(x2.contiguous(), self.qweight, self.scales, self.su, self.sv, bias, ptrs, off)
+            self.peer.barrier()
+            g = self.peer.result(x2.shape[0])
             rows = x2.shape[0]
         else:
             y = self.local(x2)

@@ -222,6 +222,14 @@ int htr_linear_gemm(const void* x, int dtype, int M, const void* qweight, int mt
                     const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* y, void* workspace,
                     size_t workspace_bytes, htr_stream_t stream);
 
+/* Row-shard form of htr_linear_gemm (one launch: batches that htr_linear_gemm would split into two are refused with
+ * HTR_ERR_TOO_LARGE): the epilogue stores row j, rows [0, m) of this shard, at element offset peer_offset + j * m of every buffer in
+ * peer_y (the gather buffers of all ranks of an NVLink box as mapped into this process, plain peer stores) instead of y; the caller
+ * then orders the ranks (htr_peer_barrier).  (No counterpart in the reference, which asserts one GPU: htr/vllm_plugin.py:91.) */
+int htr_linear_gemm_peers(const void* x, int dtype, int M, const void* qweight, int mt, int nt, int K, const void* scales,
+                          const uint8_t* su, const uint8_t* sv, const void* bias /* may be NULL */, void* const* peer_y, int npeer,
+                          int64_t peer_offset, void* workspace, size_t workspace_bytes, htr_stream_t stream);
+
 /* Original-basis weight W = Sv Ho Q Hi Su as bf16 / f16 / f32 [m, n] (debug and prefill hook).
  * Stands in for dequant_w (htr_kernels.cpp:13, k_dequant_w* htr_kernels.cu:658-903); compared with
  * wire.dequant (htr/wire.py:105-113). */

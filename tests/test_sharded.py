@@ -181,8 +181,9 @@ def _nccl_worker(rank, world, port, q):
                 ok = ok and bool(torch.equal(peer(xi), want))
         peer.peer.check()                                                    # no bounded wait ran out
         sharded_mod.PEER_ORDER = "kernel"
-        # three rows (float32 sums per window): within bf16 rounding of the single-GPU result; eight rows: local GEMM + all-gather
-        for rows in (3, 8):
+        # three rows (float32 sums per window): within bf16 rounding of the single-GPU result; eight and twenty rows: the tensor-core
+        # GEMM with the peer-store epilogue; forty rows: local GEMM + all-gather
+        for rows in (3, 8, 20, 40):
             xr = torch.randn(rows, 1024, generator=torch.Generator().manual_seed(rows)).bfloat16().to(dev)
             got, want = peer(xr).float(), ops.linear(xr, *full_w).float()
             ok = ok and float((got - want).norm() / want.norm()) <= 4e-3
