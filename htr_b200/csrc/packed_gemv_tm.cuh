@@ -22,7 +22,7 @@
 // 16-row strips, fetches those strips' tiles itself (private cp.async ring) and writes them to A stage (trip % 3).  One lane of
 // warp 8 issues the MMAs (eight per unit: K = 32 bytes = 8 weights each) and commits them onto the mbarrier that frees the
 // A stage.  Every wait on an mbarrier is bounded; on expiry the thread block records a fault word in the workspace, stops
-// issuing, lets its copies drain, frees its tensor memory and returns.
+// issuing, lets its copies and MMAs drain, writes NaN into the rows it still owed, frees its tensor memory and returns.
 //
 // Decomposition (flat unit ranges), split reduction (64-bit partial sums, last arriver finishes), epilogue and launch overlap
 // as in packed_gemv_mma.cuh.
@@ -549,6 +549,23 @@ __global__ void __launch_bounds__(kTmThreads, 2) packed_gemv_tm_kernel(const Gem
     }
   }
   if (!predecessor_done) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (s_fail) {
+    // the row blocks this thread block still owed never complete (nobody arrives for them): their rows come out as NaN, visible to
+    // any consumer, beside the fault word
+    const int rb_last = (u_end - 1) / CG;
+    const float4 nan4 = make_float4(__uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u),
+                                    __uint_as_float(0x7FC00000u));
+    for (int b = rb; b <= rb_last; ++b)
+      for (int e = tid; e < p.rows * 32; e += kTmThreads) {
+        const int r = e >> 5, row0 = b * 128 + 4 * (e & 31);
+        if (p.npeer == 0) {
+          if (row0 < p.m_out) store_quad(p.y, (size_t)r * p.m_out + row0, p.dtype, nan4);
+        } else {
+#pragma unroll 1
+          for (int pe = 0; pe < p.npeer; ++pe) store_quad(p.peer_y[pe], (size_t)p.peer_offset + (size_t)r * m + row0, p.dtype, nan4);
+        }
+      }
+  }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == kTmDecodeWarps) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kTmCols) : "memory");

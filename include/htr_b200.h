@@ -281,7 +281,8 @@ int htr_codebook_f32(float* out, htr_stream_t stream);
  * to eight rows always run on the CUDA-core GEMV.  (Measurement and test knob; no counterpart in the reference.) */
 void htr_set_gemv_kernel(int kind);
 /* Byte offset, inside the workspace of htr_linear and its variants, of a 32-bit word that the tensor-memory GEMV sets to 1 when
- * one of its bounded waits ran out (the launch then left rows of y unwritten).  Zero in a healthy run; the caller clears it. */
+ * one of its bounded waits ran out (the rows of y that the thread block still owed are then written as NaN).  Zero in a healthy run;
+ * the caller clears it. */
 size_t htr_linear_fault_offset(void);
 /* Grid size and scratch slots the next htr_linear call with these sizes would use (for tests and benches). */
 int htr_linear_plan(int M, int m, int n, int K, int* grid, int* slots_per_block);
