@@ -17,7 +17,8 @@ One JSON line is printed by rank 0:
             `stream_ordered` repeats the pass in the default form, in which each launch waits for its predecessor
   e2e       the same pass through the public operator (htr_b200.ops.linear) with the activations in pinned
             host memory and the outputs copied back to pinned host memory inside the timed region (one host->device
-            copy of a K-group's activations before its linears, one device->host copy of its outputs after them)
+            copy of a K-group's activations before its linears, one device->host copy of its outputs after them; the
+            copies of a pass run on their own streams beside the linears of the neighbouring K-groups)
   roofline  of the GEMV kernel: achieved = algorithmic packed bytes per launch / average launch duration,
             peak = measured HBM copy bandwidth (MEASURED_PEAKS.json, else the fallback 6650 GB/s)
   cpu_baseline  the CPU restatement of the reference's decode + matmul path (oracle/, OpenMP) on a bounded
