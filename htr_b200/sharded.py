@@ -404,8 +404,6 @@ class ExpertParallelMoE:
         """Combine over the ranks without a collective: the gate-weighted sum of this rank's pairs is stored into every rank's
         buffer (htr_moe_combine_peers: plain peer stores), the ranks order themselves (PEER_ORDER) and every rank adds the parts in
         rank order (htr_rank_sum), so all ranks hold the same bits."""
-        import ctypes
-
         from . import _lib, ops
 
         dev = dn.device
