@@ -171,7 +171,9 @@ __global__ void __launch_bounds__(128) attention_kernel(const __nv_bfloat16* __r
 // Single-token step: rotary embedding, cache write and attention of one query head in one kernel.  grid (heads_q), 128 threads,
 // D == 128.  The CTA rotates its query and its group's new key itself (the four query heads of a group repeat that small piece
 // of work), takes the scores and values of the new position from shared memory and those of older positions from the cache;
-// the first head of each group writes the new key and value rows.  Same roundings as rope_cache_kernel + attention_kernel.
+// the first head of each group writes the new key and value rows.  Same roundings as rope_cache_kernel + attention_kernel; the
+// weighted sum of the value rows runs over four interleaved position streams (one per warp), so it differs from theirs in the last
+// float32 bits.
 __global__ void __launch_bounds__(128) rope_attention_kernel(const __nv_bfloat16* __restrict__ qkv, const long long* __restrict__ pos,
                                                              const float* __restrict__ cosv, const float* __restrict__ sinv,
                                                              __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
@@ -209,24 +211,29 @@ __global__ void __launch_bounds__(128) rope_attention_kernel(const __nv_bfloat16
     }
   }
   __syncthreads();
+  const int lane = tid & 31, warp = tid >> 5;
   float mx = -3.0e38f;
-  for (int t = tid; t < len; t += 128) {
+  // scores of the cached positions: one thread per position (the 256-byte key row as sixteen 16-byte loads in flight)
+  for (int t = tid; t < p; t += 128) {
+    const uint4* kr = reinterpret_cast<const uint4*>(k_cache + ((size_t)t * hkv + kvh) * D);
     float d = 0.f;
-    if (t == p) {
-#pragma unroll 8
-      for (int e = 0; e < D; ++e) d += sk[e] * sq[e];
-    } else {
-      const uint4* kr = reinterpret_cast<const uint4*>(k_cache + ((size_t)t * hkv + kvh) * D);
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const uint4 raw = __ldg(kr + c);
-        const float4 q0 = *reinterpret_cast<const float4*>(sq + 8 * c), q1 = *reinterpret_cast<const float4*>(sq + 8 * c + 4);
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-        const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z)), f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
-        d += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + e.x * q1.x + e.y * q1.y + f.x * q1.z + f.y * q1.w;
-      }
+    for (int c = 0; c < 16; ++c) {
+      const uint4 raw = __ldg(kr + c);
+      const float4 q0 = *reinterpret_cast<const float4*>(sq + 8 * c), q1 = *reinterpret_cast<const float4*>(sq + 8 * c + 4);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.z)), f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.w));
+      d += a.x * q0.x + a.y * q0.y + b.x * q0.z + b.y * q0.w + e.x * q1.x + e.y * q1.y + f.x * q1.z + f.y * q1.w;
     }
     sc[t] = d;
+    mx = fmaxf(mx, d);
+  }
+  // score of the new position from shared memory: warp 0, four dimensions per lane
+  if (warp == 0) {
+    float d = sk[4 * lane] * sq[4 * lane] + sk[4 * lane + 1] * sq[4 * lane + 1] + sk[4 * lane + 2] * sq[4 * lane + 2] + sk[4 * lane + 3] * sq[4 * lane + 3];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) d += __shfl_xor_sync(0xFFFFFFFFu, d, o);
+    if (lane == 0) sc[p] = d;
     mx = fmaxf(mx, d);
   }
   mx = block_max(mx, red);
@@ -237,18 +244,35 @@ __global__ void __launch_bounds__(128) rope_attention_kernel(const __nv_bfloat16
     sum += e;
   }
   sum = block_sum(sum, red);
-  const __nv_bfloat16* vcol = v_cache + (size_t)kvh * D + tid;
-  float acc = 0.f;
-  int t = 0;
-  for (; t + 8 <= p; t += 8) {
-    float vv[8];
+  // values: warp w takes the cached positions w, w + 4, ..., a lane four dimensions of a row (one 8-byte load; a row is one
+  // coalesced 256-byte read of the warp), eight rows in flight per warp; the four partial sums meet in shared memory
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  {
+    const __nv_bfloat16* vrow = v_cache + (size_t)kvh * D + 4 * lane;
+    const size_t stride = (size_t)hkv * D;
+    int t = warp;
+    for (; t + 28 < p; t += 32) {
+      uint2 raw[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) vv[j] = bf(vcol[(size_t)(t + j) * hkv * D]);
+      for (int j = 0; j < 8; ++j) raw[j] = __ldg(reinterpret_cast<const uint2*>(vrow + (size_t)(t + 4 * j) * stride));
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc += sc[t + j] * vv[j];
+      for (int j = 0; j < 8; ++j) {
+        const float w = sc[t + 4 * j];
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[j].x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw[j].y));
+        a0 += w * lo.x; a1 += w * lo.y; a2 += w * hi.x; a3 += w * hi.y;
+      }
+    }
+    for (; t < p; t += 4) {
+      const uint2 raw = __ldg(reinterpret_cast<const uint2*>(vrow + (size_t)t * stride));
+      const float w = sc[t];
+      const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x)), hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      a0 += w * lo.x; a1 += w * lo.y; a2 += w * hi.x; a3 += w * hi.y;
+    }
   }
-  for (; t < p; ++t) acc += sc[t] * bf(vcol[(size_t)t * hkv * D]);
-  acc += sc[p] * sv[tid];
+  __shared__ __align__(16) float part[4][D];
+  *reinterpret_cast<float4*>(&part[warp][4 * lane]) = make_float4(a0, a1, a2, a3);
+  __syncthreads();
+  const float acc = part[0][tid] + part[1][tid] + part[2][tid] + part[3][tid] + sc[p] * sv[tid];
   out[(size_t)head * D + tid] = __float2bfloat16_rn(acc / sum);
 }
 
